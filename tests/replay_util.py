@@ -32,7 +32,7 @@ def run_trace(folder, dtype, steps, out_dir, max_tokens, page_size, timeout=600,
     {request: tokens it took over instead of computing}."""
     os.makedirs(out_dir, exist_ok=True)
     cmd = [sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+           "--max-tokens", str(max_tokens), "--page-size", str(page_size), "--max-requests", "8"]
     if share:
         cmd.append("--share-prefixes")
     text = "".join(json.dumps(s) + "\n" for s in steps)

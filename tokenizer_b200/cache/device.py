@@ -12,8 +12,8 @@ from .manager import CachePlan, RequestCache
 
 class DeviceCache(CachePlan):
     """`CachePlan` plus the memory.  Pool of group g:
-    [calls in the group, 2 (keys, values), pages * page_size, kv_heads, head_dim]
-    in the compute dtype; a token's keys of one call lie at row
+    [calls in the group, planes (keys, values; or one row for both), pages * page_size,
+    kv_heads, head_dim] in the compute dtype; a token's keys of one call lie at row
     page * page_size + offset."""
 
     def __init__(self, needs, num_pages: int, page_size: int, max_requests: int,
@@ -23,7 +23,7 @@ class DeviceCache(CachePlan):
         self.pools: List[torch.Tensor] = []
         for layout in self.groups:
             self.pools.append(torch.zeros(
-                (len(layout.calls), 2, num_pages * page_size, layout.kv_heads, layout.head_dim),
+                (len(layout.calls), layout.planes, num_pages * page_size, layout.kv_heads, layout.head_dim),
                 dtype=runtime.dtype, device=runtime.device))
         self.states = {}
         for call in self.state_calls:
@@ -36,6 +36,11 @@ class DeviceCache(CachePlan):
         for arena in self.states.values():
             arena[cache.state_slot].zero_()
 
+    def on_release(self, cache: RequestCache) -> None:
+        if cache.length:            # a request that is recomputed from its first token starts from zero
+            for arena in self.states.values():
+                arena[cache.state_slot].zero_()
+
     def bindings(self, order) -> List[CacheBinding]:
         """One binding per call of the order."""
         out = []
@@ -47,11 +52,11 @@ class DeviceCache(CachePlan):
                 layer = self.groups[group].calls.index(source)
                 binding.group = group
                 binding.k_pool = self.pools[group][layer, 0]
-                binding.v_pool = self.pools[group][layer, 1]
+                binding.v_pool = self.pools[group][layer, 1] if self.groups[group].planes > 1 else None
             binding.state = self.states.get(source)
             out.append(binding)
         return out
 
     def bytes_per_token(self) -> int:
         size = torch.empty((), dtype=self.runtime.dtype).element_size()
-        return sum(len(g.calls) * 2 * g.kv_heads * g.head_dim * size for g in self.groups)
+        return sum(len(g.calls) * g.planes * g.kv_heads * g.head_dim * size for g in self.groups)

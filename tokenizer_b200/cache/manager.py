@@ -29,6 +29,7 @@ class GroupLayout:
     kv_heads: int
     head_dim: int
     window: Optional[int]
+    planes: int = 2                                  # rows a token stores per call (keys and values, or one for both)
     calls: List[int] = field(default_factory=list)   # calls of the order that write here
 
 
@@ -49,7 +50,8 @@ class RequestCache:
 
 
 def plan_groups(needs) -> (List[GroupLayout], List[Optional[int]]):
-    """Group the calls by what their mixer stores per token.  Returns the
+    """Group the calls by what their mixer stores per token (kv heads, head size, window, and
+    whether keys and values are two rows or one).  Returns the
     groups and, for each call, its group (None for a call without keys)."""
     groups: List[GroupLayout] = []
     group_of: List[Optional[int]] = []
@@ -57,9 +59,9 @@ def plan_groups(needs) -> (List[GroupLayout], List[Optional[int]]):
         if need is None or need.kv is None:
             group_of.append(None)
             continue
-        key = (need.kv.kv_heads, need.kv.head_dim, need.kv.window)
+        key = (need.kv.kv_heads, need.kv.head_dim, need.kv.window, need.kv.planes)
         for g, layout in enumerate(groups):
-            if (layout.kv_heads, layout.head_dim, layout.window) == key:
+            if (layout.kv_heads, layout.head_dim, layout.window, layout.planes) == key:
                 break
         else:
             groups.append(GroupLayout(*key))
@@ -188,9 +190,13 @@ class CachePlan:
         if cache.published is None:
             cache.published = False
 
+    def on_release(self, cache: RequestCache) -> None:
+        """Hook for the device side (a state that starts from zero again)."""
+
     def release_pages(self, cache: RequestCache) -> None:
         """Give back every page (the request stays open with nothing stored):
-        what preemption does before a later recompute."""
+        what preemption does before a later recompute.  Per-request state starts anew too."""
+        self.on_release(cache)
         for g, allocator in enumerate(self.allocators):
             for page in cache.tables[g]:
                 if page >= 0:

@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to its typed configuration.
 
-`config.json["architectures"][0]` chooses the entry everywhere: loading a
+`config.json["architectures"][0]` (or `"architecture"`) chooses the entry everywhere: loading a
 folder, random weights, replay, generation.  An entry is the configuration
 class; the class reads its own keys (`from_dict`) and describes the model as a
 `ModelSpec` (`model_spec`), from which the generic decoder is assembled.
@@ -38,8 +38,10 @@ def config_class_for(name: str) -> Type:
 
 def config_from_dict(raw: Dict[str, Any]):
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]           # some designs name themselves with one string
     if not isinstance(names, list) or not names or not isinstance(names[0], str):
-        raise ConfigError('config.json needs "architectures": ["<name>"]')
+        raise ConfigError('config.json needs "architectures": ["<name>"] (or "architecture": "<name>")')
     return config_class_for(names[0]).from_dict(raw)
 
 

@@ -110,7 +110,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ row_req, const int* __restrict__ pos, int nh,
                         int nkv, int page, int window, float scale,
                         float* __restrict__ scratch, int* __restrict__ counters, int min_chunk,
-                        const int* __restrict__ rows) {
+                        const int* __restrict__ rows, const float* __restrict__ sink) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
   __shared__ int is_last;
   // The rows' requests, positions and block tables were written before the predecessor (the
@@ -389,6 +389,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       piece[c] = num;
       if (c == 0) { piece[HEAD_DIM] = m; piece[HEAD_DIM + 1] = den; }
     } else if (n_splits == 1) {
+      if (sink) den += exp2f(sink[kvh * group + head] * 1.4426950408889634f - m);   // the sink: once, unscaled
       out[((size_t)row * nh + kvh * group + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
     } else {
       float* piece = base + head * per_head + (size_t)split * kRow;
@@ -407,7 +408,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const float l_s = on ? dec_peer_load(piece + HEAD_DIM + 1, (unsigned)lane) : 0.f;
         const float m_all = warp_max(m_s);
         const float f = exp2f(m_s - m_all);                 // 0 for lanes without a piece
-        const float den = warp_sum(f * l_s);
+        float den = warp_sum(f * l_s);
+        if (sink) den += exp2f(sink[kvh * group + head] * 1.4426950408889634f - m_all);
         for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
           const int c = c0 + lane;
           const bool have = c < HEAD_DIM;
@@ -445,7 +447,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const float l_s = on ? __ldcg(&pieces[(size_t)lane * kRow + HEAD_DIM + 1]) : 0.f;
     const float m_all = warp_max(m_s);
     const float f = exp2f(m_s - m_all);                   // 0 for lanes without a split
-    const float den = warp_sum(f * l_s);
+    float den = warp_sum(f * l_s);
+    if (sink) den += exp2f(sink[kvh * group + head] * 1.4426950408889634f - m_all);
     for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
       const int c = c0 + lane;
       const bool have = c < HEAD_DIM;
@@ -475,7 +478,7 @@ TOKB200_API int tokb200_decode_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, int n_rows, int nh, int nkv, int d,
     int page, int window, float scale, float* scratch, int* counters, const int* rows,
-    cudaStream_t stream) {
+    const float* sink, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > DEC_MAX_GROUP || page <= 0 ||
       nkv > 65535 || n_rows > 65535)
@@ -545,7 +548,8 @@ TOKB200_API int tokb200_decode_attention(
   // pieces of up to two passes: the first tiles before the wait (see EARLY)
   const bool early = min_chunk <= 2 * DEC_BLOCK_KEYS;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
-                 int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*) =
+                 int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*,
+                 const float*) =
       early ? (cluster ? decode_attention_kernel<true, true> : decode_attention_kernel<false, true>)
             : (cluster ? decode_attention_kernel<true, false> : decode_attention_kernel<false, false>);
   if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
@@ -564,7 +568,7 @@ TOKB200_API int tokb200_decode_attention(
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                             table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                            counters, min_chunk, rows);
+                            counters, min_chunk, rows, sink);
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = dim3(DEC_THREADS);
@@ -586,6 +590,6 @@ TOKB200_API int tokb200_decode_attention(
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                        (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                                        table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                                       counters, min_chunk, rows);
+                                       counters, min_chunk, rows, sink);
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }

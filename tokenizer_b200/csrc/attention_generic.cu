@@ -10,6 +10,10 @@
 // fixed chunks of ATT_CHUNK counted from lo, so a row's arithmetic depends only on
 // its own position and window, never on the batch around it.  Scores, the
 // running maximum, the exponentials and the weighted sum are 32-bit.
+//
+// `sink` (optional, one float32 per query head): a learned score without key or value that
+// takes part in the softmax's denominator once, unscaled: the running maximum starts at it
+// and the running sum at 1.
 #include "common.cuh"
 
 #define ATT_THREADS 128
@@ -22,7 +26,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const T* __restrict__ v_pool, T* __restrict__ out,
                                const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ row_req, const int* __restrict__ pos,
-                               int nh, int nkv, int d, int page, int window, float scale) {
+                               int nh, int nkv, int d, int page, int window, float scale,
+                               const float* __restrict__ sink) {
   extern __shared__ float smem[];
   float* q_s = smem;                 // d
   float* p_s = smem + d;             // ATT_CHUNK
@@ -41,7 +46,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   for (int i = threadIdx.x; i < d; i += ATT_THREADS) q_s[i] = to_float(q_row[i]);
   __syncthreads();
 
-  float m = -INFINITY, l = 0.f;
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   float acc[ATT_MAX_HEAD_DIM / ATT_THREADS];
 #pragma unroll
   for (int i = 0; i < ATT_MAX_HEAD_DIM / ATT_THREADS; ++i) acc[i] = 0.f;
@@ -91,7 +96,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 TOKB200_API int tokb200_paged_attention_generic(
     const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
     const int* block_table, int table_stride, const int* row_req, const int* pos, int n_rows,
-    int nh, int nkv, int d, int page, int window, float scale, cudaStream_t stream) {
+    int nh, int nkv, int d, int page, int window, float scale, const float* sink,
+    cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d <= 0 || d > ATT_MAX_HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 ||
       nh > 65535)
@@ -101,12 +107,12 @@ TOKB200_API int tokb200_paged_attention_generic(
   if (dtype == TOKB200_F32)
     paged_attention_generic_kernel<float><<<grid, ATT_THREADS, smem, stream>>>(
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table,
-        table_stride, row_req, pos, nh, nkv, d, page, window, scale);
+        table_stride, row_req, pos, nh, nkv, d, page, window, scale, sink);
   else if (dtype == TOKB200_BF16)
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, nh, nkv, d, page, window,
-        scale);
+        scale, sink);
   else
     return TOKB200_BAD_DTYPE;
   return tokb200_launch_status();

@@ -106,7 +106,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page,
-                         int window, float scale_log2) {
+                         int window, float scale_log2, const float* __restrict__ sink) {
   extern __shared__ __align__(16) __nv_bfloat16 smem[];
   __nv_bfloat16* q_s = smem;                       // [64][kStride]
   __nv_bfloat16* k_s = q_s + kTile;                // PF_STAGES tiles
@@ -299,7 +299,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (my_row[i] >= n_rows) continue;
-    const float inv = 1.0f / l_run[i];
+    // a sink takes part in the denominator once, unscaled (it has no key and no value)
+    const float extra = sink ? exp2f(sink[h] * 1.4426950408889634f - m_run[i] * scale_log2) : 0.f;
+    const float inv = 1.0f / (l_run[i] + extra);
     __nv_bfloat16* dst = out + ((size_t)(row0 + my_row[i]) * nh + h) * HEAD_DIM;
 #pragma unroll
     for (int nt = 0; nt < HEAD_DIM / 8; ++nt) {
@@ -315,7 +317,7 @@ TOKB200_API int tokb200_prefill_attention_head_dim() { return HEAD_DIM; }
 TOKB200_API int tokb200_prefill_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
-    int nkv, int d, int page, int window, float scale, cudaStream_t stream) {
+    int nkv, int d, int page, int window, float scale, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || nh > 65535)
     return TOKB200_BAD_SIZE;
@@ -336,6 +338,6 @@ TOKB200_API int tokb200_prefill_attention(
   prefill_attention_kernel<<<grid, PF_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
       (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, tiles, n_tiles, nh, nkv, page,
-      window, scale_log2);
+      window, scale_log2, sink);
   return tokb200_launch_status();
 }

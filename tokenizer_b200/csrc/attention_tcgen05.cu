@@ -201,7 +201,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page, int window,
-                         float scale_log2) {
+                         float scale_log2, const float* __restrict__ sink) {
   extern __shared__ __align__(1024) unsigned char fa_raw[];      // swizzle atoms: 1024-byte aligned
   unsigned char* q_s = fa_raw;
   unsigned char* k_s = q_s + kQBytes;                            // FA_KV_BUFFERS buffers
@@ -471,6 +471,8 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       weight[j] = m_j == -INFINITY ? 0.f : fa_exp2((m_j - m_all) * scale_log2);
       den += weight[j] * stat_s[(j * FA_ROWS + r) * 2 + 1];
     }
+    // a sink takes part in the denominator once, unscaled (it has no key and no value)
+    if (sink && m_all > -INFINITY) den += exp2f(sink[h] * 1.4426950408889634f - m_all * scale_log2);
     if (ok) {
       const float inv = 1.0f / den;
       __nv_bfloat16* dst = out + ((size_t)(row0 + min(r, n_rows - 1)) * nh + h) * HEAD_DIM + split * kSlice;
@@ -526,7 +528,7 @@ TOKB200_API int tokb200_attention_tcgen05_error(void) {
 TOKB200_API int tokb200_attention_tcgen05(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
-    int nkv, int d, int page, int window, float scale, cudaStream_t stream) {
+    int nkv, int d, int page, int window, float scale, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0)
     return TOKB200_BAD_SIZE;
@@ -553,5 +555,5 @@ TOKB200_API int tokb200_attention_tcgen05(
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table, table_stride,
                           row_req, pos, tiles, n_tiles, nh, nkv, page, window,
-                          scale * 1.4426950408889634f);
+                          scale * 1.4426950408889634f, sink);
 }

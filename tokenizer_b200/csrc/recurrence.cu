@@ -1,0 +1,113 @@
+// Gated linear recurrences over the rows of a step, with the state carried per request.
+//
+// minGRU: per channel c and token t
+//     z = sigmoid(zp[t,c]),  cand = u >= 0 ? u + 1/2 : sigmoid(u)   (u = up[t,c]),
+//     S_t = (1 - z) S_(t-1) + z cand,      y[t,c] = S_t * silu(g[t,c]),
+// where zp, up and g are three column ranges of one projection's output (the projection adds
+// the biases).  The state S is float32 [slots, width]; a request's rows are consecutive
+// (q_start[r] .. q_start[r+1]) and its state lives in slot state_slot[r]: read before the
+// request's first row of the step, written back after its last.  Gates, candidate, state and
+// the product with silu(g) are 32-bit whatever the type of the projection's output.
+//
+// A step's rows of one request are taken in runs of TY * K tokens: thread (x, y) of a block owns
+// channel x of the block's 32 and K consecutive tokens; it folds them into one affine map
+// S -> P S + B, the maps of the block's TY threads of a channel are chained through shared
+// memory, and every thread then walks its K tokens again from the state it was handed, out of
+// registers.  Every input is read once.  A step of single tokens runs with TY = 1, K = 1.
+#include "common.cuh"
+
+#define REC_CHANNELS 32
+#define REC_MAX_TY 32
+
+__device__ __forceinline__ float rec_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+template <typename TI, typename TO, int K>
+__global__ void __launch_bounds__(REC_CHANNELS * REC_MAX_TY)
+min_gru_scan_kernel(const TI* __restrict__ proj, int ld, int z_at, int u_at, int g_at, int width,
+                    float* __restrict__ state, const int* __restrict__ q_start,
+                    const int* __restrict__ state_slot, TO* __restrict__ out) {
+  __shared__ float p_s[REC_MAX_TY][REC_CHANNELS + 1];
+  __shared__ float b_s[REC_MAX_TY][REC_CHANNELS + 1];
+  __shared__ float carry_s[REC_CHANNELS];
+  const int x = threadIdx.x, y = threadIdx.y, ty = blockDim.y;
+  const int c = blockIdx.x * REC_CHANNELS + x;
+  const int r = blockIdx.y;
+  const bool live = c < width;
+  // the spans and slots were written before the predecessor started
+  const int first = q_start[r], last = q_start[r + 1];
+  const int slot = state_slot[r];
+  pdl_wait();
+  pdl_launch();
+  if (first >= last || slot < 0) return;
+  if (y == 0) carry_s[x] = live ? state[(size_t)slot * width + c] : 0.f;
+  __syncthreads();
+  for (int t0 = first; t0 < last; t0 += ty * K) {
+    const int mine = t0 + y * K;
+    float a[K], b[K], gate[K];
+    float p = 1.f, acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int t = mine + k;
+      if (live && t < last) {
+        const TI* row = proj + (size_t)t * ld;
+        const float z = rec_sigmoid(to_float(row[z_at + c]));
+        const float u = to_float(row[u_at + c]);
+        const float g = to_float(row[g_at + c]);
+        const float cand = u >= 0.f ? u + 0.5f : rec_sigmoid(u);
+        a[k] = 1.0f - z;
+        b[k] = z * cand;
+        gate[k] = g * rec_sigmoid(g);
+      } else {
+        a[k] = 1.f; b[k] = 0.f; gate[k] = 0.f;
+      }
+      acc = a[k] * acc + b[k];
+      p *= a[k];
+    }
+    float s = carry_s[x];
+    if (ty > 1) {
+      p_s[y][x] = p;
+      b_s[y][x] = acc;
+      __syncthreads();
+      for (int i = 0; i < y; ++i) s = p_s[i][x] * s + b_s[i][x];
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int t = mine + k;
+      s = a[k] * s + b[k];
+      if (live && t < last) out[(size_t)t * width + c] = from_float<TO>(s * gate[k]);
+    }
+    if (ty > 1) __syncthreads();       // every thread has read the carry and the maps
+    if (y == ty - 1) carry_s[x] = s;
+    if (ty > 1) __syncthreads();
+  }
+  if (y == ty - 1 && live) state[(size_t)slot * width + c] = carry_s[x];
+}
+
+// proj: [rows, ld] (float32 or bfloat16) with the three column ranges starting at z_at, u_at,
+// g_at, each `width` wide; out: [rows, width] dense.  `longest`: the most rows a request brings
+// to the step (chooses the shape of a block).
+TOKB200_API int tokb200_min_gru_scan(const void* proj, int proj_dtype, int ld, int z_at, int u_at,
+                                     int g_at, int width, float* state, const int* q_start,
+                                     const int* state_slot, int n_requests, int longest, void* out,
+                                     int out_dtype, cudaStream_t stream) {
+  if (n_requests <= 0 || longest <= 0) return TOKB200_OK;
+  if (width <= 0 || ld < width || n_requests > 65535) return TOKB200_BAD_SIZE;
+  dim3 grid((width + REC_CHANNELS - 1) / REC_CHANNELS, n_requests);
+  int ty = 1;
+  while (ty < REC_MAX_TY && ty * 4 < longest) ty *= 2;
+  const bool single = longest == 1;
+  dim3 block(REC_CHANNELS, single ? 1 : ty);
+#define LAUNCH(TI, TO)                                                                              \
+  return single ? launch_dependent(min_gru_scan_kernel<TI, TO, 1>, grid, block, 0, stream,         \
+                                   (const TI*)proj, ld, z_at, u_at, g_at, width, state, q_start,  \
+                                   state_slot, (TO*)out)                                            \
+                : launch_dependent(min_gru_scan_kernel<TI, TO, 4>, grid, block, 0, stream,         \
+                                   (const TI*)proj, ld, z_at, u_at, g_at, width, state, q_start,  \
+                                   state_slot, (TO*)out)
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return TOKB200_BAD_DTYPE;
+}

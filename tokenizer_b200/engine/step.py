@@ -96,7 +96,10 @@ class Engine:
         self.use_graphs = bool(use_graphs) and model.graph_safe()
         self._graphs = {}
         self._graph_buffer = 0
-        tables = sum(max_requests * (model.max_positions // page_size + 8) for _ in self.cache.groups)
+        # block tables reach as far as a request's positions: no further than the pool holds where a
+        # model has no longest position worth the name (a table that outgrows this moves the buffer once)
+        reach = min(model.max_positions, max(num_pages * page_size, 4096))
+        tables = sum(max_requests * (reach // page_size + 8) for _ in self.cache.groups)
         self.builder.reserve_capacity(16 * 8192 + tables)
 
     @classmethod

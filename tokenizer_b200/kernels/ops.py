@@ -306,8 +306,18 @@ def silu_gate(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> 
         "silu_gate")
 
 
+def _sink(sink, nh):
+    """A softmax sink: one float32 per query head, or None."""
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nh):
+        raise ValueError("attention: a sink is one float32 per query head")
+    return _ptr(sink)
+
+
 def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page,
-                            window, scale) -> None:
+                            window, scale, sink: Optional[torch.Tensor] = None) -> None:
+    """`sink` (float32, one per query head): a score without key or value that counts once in
+    the softmax's denominator, unscaled.  `v_pool` may be `k_pool` itself (values that are the
+    leading lanes of the key rows)."""
     if d > 512:
         raise ValueError(f"attention: head size {d} is beyond 512")
     if nh % nkv:
@@ -315,7 +325,7 @@ def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, n
     _check(_lib("attention_generic").tokb200_paged_attention_generic(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _i(_tag(q)), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(q.shape[0]), _i(nh), _i(nkv),
-        _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
+        _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _sink(sink, nh), _stream()),
         "paged_attention")
 
 
@@ -378,7 +388,7 @@ def decode_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page, window,
-                     scale, rows: Optional[torch.Tensor] = None) -> None:
+                     scale, rows: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> None:
     """Attention for rows of one token each (bfloat16): keys are split over
     blocks and merged; the scratch for the pieces is kept per (device, rows,
     heads, head size) and reused by every layer, which run one after another.  With `rows`
@@ -401,7 +411,7 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
         _i(page), _i(-1 if window is None else int(window)), _f(scale), _ptr(scratch),
-        _ptr(counters), _ptr(rows), _stream()), "decode_attention")
+        _ptr(counters), _ptr(rows), _sink(sink, nh), _stream()), "decode_attention")
 
 
 _stream_plans = {}
@@ -529,7 +539,7 @@ def prefill_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv,
-                      d, page, window, scale) -> None:
+                      d, page, window, scale, sink: Optional[torch.Tensor] = None) -> None:
     """Attention for portions of prompts (bfloat16).  `tiles` is int32 [n, 2]:
     (first row, rows <= 64) of consecutive rows of one request."""
     if q.dtype != torch.bfloat16:
@@ -540,8 +550,8 @@ def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
     _check(lib.tokb200_prefill_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
-        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
-        "prefill_attention")
+        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _sink(sink, nh),
+        _stream()), "prefill_attention")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -774,7 +784,7 @@ def attention_tcgen05_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv, d,
-                      page, window, scale) -> None:
+                      page, window, scale, sink: Optional[torch.Tensor] = None) -> None:
     """Attention for portions of prompts on tcgen05 (bfloat16, head size 64 or 128).
     `tiles` is int32 [n, 2]: (first row, rows <= 128) of consecutive rows of one request."""
     if q.dtype != torch.bfloat16:
@@ -785,8 +795,8 @@ def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
     _check(lib.tokb200_attention_tcgen05(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
-        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
-        "attention_tcgen05")
+        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _sink(sink, nh),
+        _stream()), "attention_tcgen05")
 
 
 def attention_tcgen05_check(d: int) -> None:
@@ -982,6 +992,84 @@ def linear_ring_gated(x, w, out, activation: str = "silu") -> None:
     _check(_lib("linear_ring").tokb200_linear_ring_gated(
         _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _i(activation_tag(activation)), _stream()),
         "linear_ring_gated")
+
+
+# ---- a gated recurrence, row-wise activations and gates, the kernels around a cached latent ----
+def _ld(t: torch.Tensor) -> int:
+    """Elements between the rows of a matrix whose rows are dense (a column slice of a wider one)."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("a matrix with dense rows is expected")
+    return t.stride(0)
+
+
+def _sliced_ptr(t: torch.Tensor):
+    if not t.is_cuda:
+        raise KernelError("tokenizer_b200 kernels run on a GPU only; got a CPU tensor")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def min_gru_scan(proj: torch.Tensor, z_at: int, u_at: int, g_at: int, width: int, state: torch.Tensor,
+                 q_start: torch.Tensor, state_slot: torch.Tensor, longest: int, out: torch.Tensor) -> None:
+    """The minGRU recurrence over a step's rows (see csrc/recurrence.cu).  `proj` [T, N] holds the
+    three pre-activations in column ranges starting at z_at, u_at, g_at; `state` float32
+    [slots, width] is read and written in place; `out` [T, width] dense."""
+    if state.dtype != torch.float32 or state.shape[-1] != width or tuple(out.shape) != (proj.shape[0], width):
+        raise ValueError("min_gru_scan: state is float32 [slots, width], out [T, width]")
+    if max(z_at, u_at, g_at) + width > proj.shape[1]:
+        raise ValueError("min_gru_scan: the column ranges leave the projection")
+    _check(_lib("recurrence").tokb200_min_gru_scan(
+        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(z_at), _i(u_at), _i(g_at), _i(width), _ptr(state),
+        _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _i(longest), _ptr(out), _i(_tag(out)),
+        _stream()), "min_gru_scan")
+
+
+def poly_norm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps); `coeff`
+    float32 [4] = (a, b, c, e) on the device; `z` may be a column slice of a wider matrix."""
+    n_rows, n = z.shape
+    if coeff.dtype != torch.float32 or coeff.numel() != 4 or tuple(out.shape) != (n_rows, n):
+        raise ValueError("poly_norm: four float32 numbers, out of z's shape")
+    _check(_lib("activation").tokb200_poly_norm(
+        _sliced_ptr(z), _i(_tag(z)), _i(_ld(z)), _ptr(coeff), _ptr(out), _i(_tag(out)), _i(n_rows), _i(n),
+        _f(eps), _stream()), "poly_norm")
+
+
+def gated_delta(y: torch.Tensor, bias: Optional[torch.Tensor], pre: torch.Tensor, out: torch.Tensor) -> None:
+    """out (float32 [T, H]) = (y + bias) * sigmoid(pre): `y` is [T, H] or float32 partial sums
+    [S, T, H]; `pre` [T, H] may be a column slice of a wider matrix."""
+    n_rows, hidden = out.shape
+    if out.dtype != torch.float32 or tuple(pre.shape) != (n_rows, hidden):
+        raise ValueError("gated_delta: out is float32 [T, H], the gate's pre-activation [T, H]")
+    n_partials, stride = _partials(y, out)
+    _check(_lib("activation").tokb200_gated_delta(
+        _ptr(y), _i(_tag(y)), _i(n_partials), _ll(stride), _ptr(bias), _sliced_ptr(pre), _i(_tag(pre)),
+        _i(_ld(pre)), _ptr(out), _i(n_rows), _i(hidden), _stream()), "gated_delta")
+
+
+def latent_prepare(proj: torch.Tensor, q_at: int, q_rank: int, c_at: int, kv_rank: int, rot_dim: int,
+                   rot_dims: int, q_gain, c_gain, eps: float, inv_freq, pos, row_req, slot, q_latent, pool) -> None:
+    """From one projection's rows: the normed query latent (dense, `q_latent` [T, q_rank]) and the
+    token's cache row in `pool` [slots, 1, row]: the normed key/value latent and, behind it, the
+    positional key part rotated at the token's position (see csrc/latent.cu).  `slot` None: no
+    cache write."""
+    if pool.dtype != q_latent.dtype or tuple(q_latent.shape) != (proj.shape[0], q_rank):
+        raise ValueError("latent_prepare: the query latent is [T, q_rank] in the cache's type")
+    _check(_lib("latent").tokb200_latent_prepare(
+        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(q_at), _i(q_rank), _i(c_at), _i(kv_rank), _i(rot_dim),
+        _i(rot_dims), _ptr(q_gain), _ptr(c_gain), _f(eps), _ptr(inv_freq), _ptr(pos), _ptr(row_req), _ptr(slot),
+        _ptr(q_latent), _ptr(pool), _i(pool.shape[-1] * pool.shape[-2]), _i(_tag(pool)), _i(proj.shape[0]),
+        _stream()), "latent_prepare")
+
+
+def rotate_interleaved(x: torch.Tensor, heads: int, lane0: int, dims: int, inv_freq, pos, row_req) -> None:
+    """Rotary encoding in place on lanes lane0 .. lane0 + dims of every head of x [T, heads * row],
+    lane 2i paired with lane 2i + 1, angle = position * inv_freq[i] (float32)."""
+    n_rows, width = x.shape
+    if width % heads:
+        raise ValueError("rotate_interleaved: the row does not divide into the heads")
+    _check(_lib("latent").tokb200_rotate_interleaved(
+        _ptr(x), _i(_tag(x)), _i(heads), _i(width // heads), _i(lane0), _i(dims), _ptr(inv_freq), _ptr(pos),
+        _ptr(row_req), _i(n_rows), _stream()), "rotate_interleaved")
 
 
 # ---- read-only streams in the decoding kernels' access patterns (bench.py --stream-probe) ----

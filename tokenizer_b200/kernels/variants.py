@@ -17,6 +17,9 @@ def all_variants():
         ("linear_stream.cu", (), ()),
         ("stream_probe.cu", (), ()),
         ("linear_ring.cu", (), ()),
+        ("recurrence.cu", (), ()),
+        ("activation.cu", (), ()),
+        ("latent.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -1,6 +1,6 @@
 from .base import (BatchAnnotation, CacheBinding, CacheNeed, GroupView, KVNeed, ResidualStream, Runtime, StateNeed,
                    StepContext, build_part, part_class, register_part, registered)
-from . import attention, block, embedding, feed_forward, norm, position  # register the parts
+from . import attention, block, embedding, feed_forward, latent_attention, norm, position, recurrent  # register the parts
 from .linear import Linear
 from .model import DecoderModel, declared_tensors
 

@@ -129,8 +129,15 @@ _SPLIT_MIXED = os.environ.get("TOKB200_MIXED", "split") != "tiles"
 _WIDE_FROM = 96
 
 
-class GQAttention:
+class PagedAttention:
+    """What every mixer that attends over the paged cache shares: the annotations its kernels
+    want packed with a step, the kernel choice (`attend`) and its say in a captured step's key.
+    A mixer that inherits it sets `nh` (query heads), `nkv` (heads of the cache rows), `d` (lanes
+    of a cache row's head), `window` (None: all keys), `scale` and, where its softmax has one,
+    `sink` (float32, one learned score per query head that counts once in the denominator)."""
+
     graph_safe = True   # launches depend on device-side metadata only
+    sink = None
 
     def batch_annotations(self):
         return [_TILES, _WIDE_TILES, _LONG_TILES, _LONG_WIDE_TILES, _SINGLES]
@@ -145,6 +152,52 @@ class GQAttention:
         # portions with single tokens beside them launch the decoding kernel too
         return kind + "+1" if min(q_lens) == 1 else kind
 
+    def attend(self, q, out, ctx, group, cache):
+        """Choose the kernel by precision and by the shape of the batch.  A group that keeps one
+        row a token (`cache.v_pool` None) is read as keys and as values: the values are then the
+        leading lanes of the key rows, and `out` has the key rows' width."""
+        k_pool = cache.k_pool
+        v_pool = cache.v_pool if cache.v_pool is not None else cache.k_pool
+        sink = self.sink
+        if q.dtype == torch.bfloat16 and ctx.max_q_len == 1 and \
+                ops.decode_attention_supported(self.nh, self.nkv, self.d):
+            ops.decode_attention(
+                q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink)
+            return
+        wide, tiles = ctx.views.get(_WIDE_TILES.key), ctx.views.get(_TILES.key)
+        singles = ctx.views.get(_SINGLES.key)
+        if _SPLIT_MIXED and q.dtype == torch.bfloat16 and singles is not None and singles[1] > 0 and \
+                ops.decode_attention_supported(self.nh, self.nkv, self.d) and \
+                ctx.views.get(_LONG_WIDE_TILES.key) is not None and ctx.views.get(_LONG_TILES.key) is not None:
+            # a step of portions AND single tokens: the single-token rows go to the decoding kernel
+            # (keys split over blocks, the group's heads as one tile), the portions to theirs
+            ops.decode_attention(
+                q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0], sink=sink)
+            wide, tiles = ctx.views[_LONG_WIDE_TILES.key], ctx.views[_LONG_TILES.key]
+        if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
+                wide is not None and ctx.max_q_len >= _WIDE_FROM and \
+                ops.attention_tcgen05_supported(self.nh, self.nkv, self.d):
+            # long portions on the tcgen05 kernel (128-row tiles, scores in tensor memory)
+            ops.attention_tcgen05(
+                q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                wide[0], wide[1], self.nh, self.nkv, self.d, group.page_size,
+                self.window, self.scale, sink=sink)
+            return
+        if q.dtype == torch.bfloat16 and tiles is not None and \
+                ops.prefill_attention_supported(self.nh, self.nkv, self.d):
+            ops.prefill_attention(
+                q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                tiles[0], tiles[1], self.nh, self.nkv, self.d, group.page_size,
+                self.window, self.scale, sink=sink)
+            return
+        ops.paged_attention_generic(
+            q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink)
+
+
+class GQAttention(PagedAttention):
     @staticmethod
     def tensors(spec):
         p, x = spec.params, spec.prefix
@@ -303,45 +356,6 @@ class GQAttention:
         mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
         self.attend(q, mixed, ctx, group, cache)
         return self.out.forward(mixed, partials_ok=True)
-
-    def attend(self, q, out, ctx, group, cache):
-        """Choose the kernel by precision and by the shape of the batch."""
-        if q.dtype == torch.bfloat16 and ctx.max_q_len == 1 and \
-                ops.decode_attention_supported(self.nh, self.nkv, self.d):
-            ops.decode_attention(
-                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
-            return
-        wide, tiles = ctx.views.get(_WIDE_TILES.key), ctx.views.get(_TILES.key)
-        singles = ctx.views.get(_SINGLES.key)
-        if _SPLIT_MIXED and q.dtype == torch.bfloat16 and singles is not None and singles[1] > 0 and \
-                ops.decode_attention_supported(self.nh, self.nkv, self.d) and \
-                ctx.views.get(_LONG_WIDE_TILES.key) is not None and ctx.views.get(_LONG_TILES.key) is not None:
-            # a step of portions AND single tokens: the single-token rows go to the decoding kernel
-            # (keys split over blocks, the group's heads as one tile), the portions to theirs
-            ops.decode_attention(
-                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0])
-            wide, tiles = ctx.views[_LONG_WIDE_TILES.key], ctx.views[_LONG_TILES.key]
-        if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
-                wide is not None and ctx.max_q_len >= _WIDE_FROM and \
-                ops.attention_tcgen05_supported(self.nh, self.nkv, self.d):
-            # long portions on the tcgen05 kernel (128-row tiles, scores in tensor memory)
-            ops.attention_tcgen05(
-                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                wide[0], wide[1], self.nh, self.nkv, self.d, group.page_size,
-                self.window, self.scale)
-            return
-        if q.dtype == torch.bfloat16 and tiles is not None and \
-                ops.prefill_attention_supported(self.nh, self.nkv, self.d):
-            ops.prefill_attention(
-                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                tiles[0], tiles[1], self.nh, self.nkv, self.d, group.page_size,
-                self.window, self.scale)
-            return
-        ops.paged_attention_generic(
-            q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -26,6 +26,8 @@ Interfaces (duck-typed; the classes below marked "interface" document them):
                 of those names (`mixer` is the part whose cache need the cache manager
                 serves); forward(stream, ctx, cache)
   embedding     forward(ids) -> x f32 [T,H];   head  forward(stream, rows) -> logits f32
+  gate          tensors(spec); __init__(spec, store, runtime); weight, bias (a projection of a
+                sublayer's input whose sigmoid scales the sublayer's output); forward(h) -> pre
 """
 from __future__ import annotations
 
@@ -37,7 +39,7 @@ import torch
 from ..config.spec import ConfigError, PartSpec
 from ..kernels import ops
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "gate")
 _REGISTRY: Dict[str, Dict[str, Any]] = {c: {} for c in CATEGORIES}
 
 
@@ -90,13 +92,14 @@ class Runtime:
 # --------------------------------------------------------------------------- #
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values per token: `kv_heads` x `head_dim` each.  With a
-    `window`, only the last window + 1 positions are ever read, and pages
-    wholly before them are given back."""
+    """Keys and values per token: `kv_heads` x `head_dim` each (`planes` = 2), or one row of
+    that size which the mixer reads as both (`planes` = 1).  With a `window`, only the last
+    window + 1 positions are ever read, and pages wholly before them are given back."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2      # 2: keys and values; 1: one row a token that serves as both (a cached latent)
 
 
 @dataclass(frozen=True)
@@ -197,7 +200,7 @@ class CacheBinding:
 
     group: int = -1                           # index into StepContext.groups, -1: no keys
     k_pool: Optional[torch.Tensor] = None     # [pages * page_size, kv_heads, head_dim]
-    v_pool: Optional[torch.Tensor] = None
+    v_pool: Optional[torch.Tensor] = None     # None where the group keeps one row a token
     state: Optional[torch.Tensor] = None      # [state slots, *shape] float32
     writes: bool = True
 

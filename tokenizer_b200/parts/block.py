@@ -3,7 +3,12 @@ x += feed_forward(norm(x)) (reference: qwen-infer/src/model.rs:603-623).  The
 adds are left pending on the stream so the next norm performs them."""
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
+from ..weights.store import TensorSpec
 from .base import register_part
+from .linear import Linear
 
 
 class PreNormResidual:
@@ -53,3 +58,76 @@ class PreNormResidual:
 
 
 register_part("block", "pre_norm_residual", PreNormResidual)
+
+
+class ResidualGate:
+    """A gate on a sublayer's output: sigmoid(W h + b) of the sublayer's own input h, element by
+    element.  Tensors `<prefix>` (the matrix) and `<prefix>.b`.  A sublayer that can carry the
+    product in its own first product takes it over (`take_side`); else `forward` computes it."""
+
+    @staticmethod
+    def tensors(spec):
+        n = spec.params["hidden_size"]
+        return [TensorSpec(spec.prefix, (n, n)), TensorSpec(spec.prefix + ".b", (n,))]
+
+    def __init__(self, spec, store, runtime):
+        self.stored = (store.get(spec.prefix), store.get(spec.prefix + ".b"))
+        self.runtime = runtime
+        self.proj = None
+
+    def forward(self, h):
+        """The gate's pre-activation, float32 [T, hidden]."""
+        if self.proj is None:
+            self.proj = Linear(self.runtime.matrix(self.stored[0]), self.runtime.vector(self.stored[1]))
+        return self.proj.forward(h, out_dtype=torch.float32)
+
+
+class GatedPreNormResidual:
+    """x += mixer(norm1(x)) * gate1(norm1(x)); x += feed_forward(norm2(x)) * gate2(norm2(x)).  The
+    gates' products ride in the sublayers' first products where those offer it; the gated outputs
+    are float32 and stay pending on the stream, so that the next norm adds them."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_gate": "gate",
+             "feed_forward": "feed_forward", "feed_forward_norm": "norm", "feed_forward_gate": "gate"}
+
+    def __init__(self, mixer, mixer_norm, mixer_gate, feed_forward=None, feed_forward_norm=None,
+                 feed_forward_gate=None):
+        self.mixer, self.mixer_norm, self.mixer_gate = mixer, mixer_norm, mixer_gate
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        self.feed_forward_gate = feed_forward_gate
+        self._carried = {}
+        for part, gate in ((mixer, mixer_gate), (feed_forward, feed_forward_gate)):
+            take = getattr(part, "take_side", None)
+            if part is not None and take is not None:
+                take(*gate.stored)
+                self._carried[id(part)] = True
+
+    def streamed_weights(self):
+        out = []
+        for part in (self.mixer, self.feed_forward):
+            out += list(getattr(part, "streamed_weights", lambda: [])())
+        return out
+
+    def _gated(self, stream, part, gate, h, y):
+        pre = part.side_pre if id(part) in self._carried else gate.forward(h)
+        delta = torch.empty(stream.x.shape, dtype=torch.float32, device=stream.x.device)
+        ops.gated_delta(y, getattr(part, "deferred_bias", None), pre, delta)
+        stream.add(delta)
+
+    def forward(self, stream, ctx, cache):
+        h = stream.normed(self.mixer_norm)
+        self._gated(stream, self.mixer, self.mixer_gate, h, self.mixer.forward(h, ctx, cache))
+        if self.feed_forward is not None:
+            h = stream.normed(self.feed_forward_norm)
+            self._gated(stream, self.feed_forward, self.feed_forward_gate, h, self.feed_forward.forward(h))
+
+
+class GatedPreNormMixerOnly(GatedPreNormResidual):
+    """The same arrangement for a layer without a feed-forward."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_gate": "gate"}
+
+
+register_part("block", "gated_pre_norm_residual", GatedPreNormResidual)
+register_part("block", "gated_pre_norm_mixer_only", GatedPreNormMixerOnly)
+register_part("gate", "residual_gate", ResidualGate)

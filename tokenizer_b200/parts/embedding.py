@@ -9,18 +9,19 @@ from ..kernels import ops
 from ..weights.store import TensorSpec
 from .base import register_part
 from .linear import Linear
+from .norm import tensor_name
 
 
 class TokenEmbedding:
     @staticmethod
     def tensors(spec):
-        return [TensorSpec(spec.prefix + ".weight",
+        return [TensorSpec(tensor_name(spec),
                            (spec.params["vocab_size"], spec.params["hidden_size"]))]
 
     def __init__(self, spec, store, runtime):
         self.runtime = runtime
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
-        self.table = runtime.matrix(store.get(spec.prefix + ".weight"))
+        self.table = runtime.matrix(store.get(tensor_name(spec)))
 
     def forward(self, ids):
         x = self.runtime.empty(ids.shape[0], self.hidden, dtype=torch.float32)
@@ -33,7 +34,7 @@ class LMHead:
     def tensors(spec):
         if spec.params.get("tied_to"):
             return []
-        return [TensorSpec(spec.prefix + ".weight",
+        return [TensorSpec(tensor_name(spec),
                            (spec.params["vocab_size"], spec.params["hidden_size"]))]
 
     def __init__(self, spec, store, runtime, tied_table=None):
@@ -43,7 +44,7 @@ class LMHead:
                 raise ValueError("a tied head needs the embedding table")
             self.proj = Linear(tied_table)
         else:
-            self.proj = Linear(runtime.matrix(store.get(spec.prefix + ".weight")))
+            self.proj = Linear(runtime.matrix(store.get(tensor_name(spec))))
 
     def forward(self, h):
         return self.proj.forward(h, out_dtype=torch.float32)

@@ -13,6 +13,7 @@ from ..kernels import ops
 from ..weights.store import TensorSpec
 from .base import register_part
 from .linear import Linear
+from .recurrent import SideProjection
 
 
 # TOKB200_FFN=separate runs the feed-forward of few rows as norm, gate/up and down kernels
@@ -104,4 +105,47 @@ class GatedMLP:
         return self.down.forward(act, partials_ok=True)
 
 
+class PolyNormMLP(SideProjection):
+    """Dense feed-forward down(act(up(h) + b_up)) + b_down with the PolyNorm activation: for a
+    token's vector z, a N(z) + b N(z^2) + c N(z^3) + e, powers taken element by element and
+    N(v) = v / sqrt(mean(v^2) + eps) over the vector; the four numbers are a tensor of the model.
+    The mean squares and the sum are 32-bit (`csrc/activation.cu`).  With a side projection taken
+    (`take_side`), the down product's bias is left to the consumer (`deferred_bias`), so that the
+    product may come as partial sums."""
+
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        return [TensorSpec(x + ".up", (p["inner_size"], p["hidden_size"])), TensorSpec(x + ".up.b", (p["inner_size"],)),
+                TensorSpec(x + ".down", (p["hidden_size"], p["inner_size"])),
+                TensorSpec(x + ".down.b", (p["hidden_size"],)), TensorSpec(x + ".act", (4,), "normal", 0.5)]
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        self.runtime = runtime
+        self.inner, self.eps = int(p["inner_size"]), float(p["eps"])
+        self._own = ([store.get(x + ".up")], [store.get(x + ".up.b")])
+        self.up = self._stack(runtime, list(self._own[0]), list(self._own[1]), None)
+        self.down = Linear(runtime.matrix(store.get(x + ".down")), runtime.vector(store.get(x + ".down.b")))
+        self.coeff = runtime.vector(store.get(x + ".act"))
+        self.deferred_bias = None
+
+    def take_side(self, weight, bias):
+        self.up = self._stack(self.runtime, list(self._own[0]), list(self._own[1]), (weight, bias))
+        self.deferred_bias = self.down.bias
+
+    def streamed_weights(self):
+        return [self.up.weight, self.down.weight]
+
+    def forward(self, h):
+        z = self.up.forward(h, out_dtype=torch.float32)
+        act = self.runtime.empty(h.shape[0], self.inner)
+        ops.poly_norm(z[:, :self.inner], self.coeff, self.eps, act)
+        self._keep_side(z)
+        if self.deferred_bias is not None:
+            return self.down.forward(act, use_bias=False, partials_ok=True)
+        return self.down.forward(act)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "poly_norm_mlp", PolyNormMLP)

@@ -9,16 +9,27 @@ from ..weights.store import TensorSpec
 from .base import register_part
 
 
+def tensor_name(spec) -> str:
+    """Where a part with one tensor finds it: `params["tensor"]` where the file names it
+    outright, else `<prefix>.weight`."""
+    return spec.params.get("tensor") or spec.prefix + ".weight"
+
+
 class RMSNorm:
+    """`gain_scale` (optional): a constant folded into the gain in float32, for a model whose
+    logits are the head's product times a constant (the final norm carries it)."""
+
     @staticmethod
     def tensors(spec):
-        return [TensorSpec(spec.prefix + ".weight", (spec.params["size"],), "one_plus_normal")]
+        return [TensorSpec(tensor_name(spec), (spec.params["size"],), "one_plus_normal")]
 
     def __init__(self, spec, store, runtime):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.runtime = runtime
-        self.gain = runtime.vector(store.get(spec.prefix + ".weight"))
+        self.gain = runtime.vector(store.get(tensor_name(spec)))
+        if spec.params.get("gain_scale") is not None:
+            self.gain = (self.gain * float(spec.params["gain_scale"])).contiguous()
 
     def folded(self):
         """(gain, eps) for a consumer that computes this norm inside its own kernel."""

@@ -31,4 +31,25 @@ class RotaryHalfSplit:
         return (self.theta, self.rotary_dim, self.max_positions)
 
 
+class RotaryInterleaved:
+    """Rotary position encoding, interleaved form: lane 2i of the rotated lanes pairs with lane
+    2i + 1, i < dims / 2; the pair (u, v) at position p becomes (u cos a - v sin a, v cos a +
+    u sin a), a = float32(p) * f_i, f_i = base^(-2i / dims) computed in float64 and stored in
+    float32.  There are no tables and no longest position: the kernels that rotate take the
+    frequencies and compute sine and cosine of the 32-bit angle themselves."""
+
+    @staticmethod
+    def tensors(spec):
+        return []
+
+    def __init__(self, spec, store, runtime):
+        self.base = float(spec.params["base"])
+        self.dims = int(spec.params["dims"])
+        if self.dims % 2 or self.dims <= 0 or self.base <= 0:
+            raise ConfigError(f"rotary width {self.dims} must be even and positive, the base positive")
+        freq = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        self.inv_freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+
 register_part("position", "rope_half_split", RotaryHalfSplit)
+register_part("position", "rope_interleaved", RotaryInterleaved)
