@@ -44,7 +44,8 @@ def run_trace(folder, dtype, steps, out_dir, max_tokens, page_size, timeout=600,
         for line in proc.stdout.splitlines():
             if line.startswith("adopted "):
                 adopted[line.split()[1]] = int(line.split()[2])
-    vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
+    config = json.load(open(os.path.join(folder, "config.json")))
+    vocab = config["vocab_size"] if "vocab_size" in config else config["vocab"]
     out = {}
     for s in steps:
         wanted = sum(len(e.get("want", [])) for e in s["entries"])
