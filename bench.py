@@ -3,7 +3,7 @@
 weights on one B200.  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 0.5b|1.5b-mixed|7b]
+                    [--config 0.5b|1.5b-mixed|7b|pufuzen]
 
 A "step" is one decode step of the whole batch.  `value` is decoded tokens a
 second timed on the device over K steps that never return to the host
@@ -196,9 +196,11 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b"],
+    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen"],
                         help="0.5b: the headline line; 7b: the same at Qwen2.5-7B sizes with 8,192-token "
-                             "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes")
+                             "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes; "
+                             "pufuzen: prefill and decoding of the Pufuzen design at two widths beside Qwen2 at "
+                             "equal width, depth and parameters, and its kernels alone")
     parser.add_argument("--context", type=int, default=8192, help="--config 7b: tokens held before decoding")
     parser.add_argument("--layer-phases", action="store_true",
                         help="print where the time of the whole-layer kernel (TOKB200_LAYER=fused) goes, phase by "
@@ -233,6 +235,8 @@ def main():
         return run_7b(args)
     if args.config == "1.5b-mixed":
         return run_mixed(args)
+    if args.config == "pufuzen":
+        return run_pufuzen(args)
     args.steps = max(1, min(args.steps, NEW_TOKENS - args.warmup - 1))
 
     import torch
@@ -654,6 +658,211 @@ def run_7b(args):
         "points_ms": {f"decode_b{b}": r["ms_per_step"] for b, r in results.items()},
     }
     print(json.dumps(line))
+    return 0
+
+
+# ---- the Pufuzen design beside the Qwen2 decoder at equal width, depth and parameter count ----
+PUFUZEN_SIZES = {
+    # width, heads, dim / vdim of a head, query and key/value latents, positional lanes, recurrence width,
+    # feed-forward width; `qwen_inner`: the gated feed-forward width that gives the Qwen2 model of the same
+    # width, depth and heads about the same parameters a layer
+    "1k": dict(width=1024, heads=16, dim=64, vdim=64, q_rank=384, kv_rank=128, kv_rank_rot=96, rot_dim=32,
+               gru=2048, ff=2816, vocab=32000, layers=8, window=1024, qwen_head_dim=64, qwen_inner=2432),
+    "2k": dict(width=2048, heads=16, dim=128, vdim=128, q_rank=768, kv_rank=128, kv_rank_rot=96, rot_dim=32,
+               gru=4096, ff=5632, vocab=32000, layers=8, window=1024, qwen_head_dim=128, qwen_inner=4864),
+}
+
+
+def pufuzen_config(z):
+    """Layers in the pattern recurrence, windowed latent attention, rotary latent attention with a
+    sink, recurrence; the attention layers carry the feed-forward."""
+    import tokenizer_b200 as tb
+    dense = {"kind": "dense", "ff": z["ff"]}
+    gru = {"type": "mingru", "mixer": {"width": z["gru"]}, "mlp": None}
+    common = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "q_rank": z["q_rank"]}
+    windowed = {"type": "latent_attention", "mlp": dense,
+                "mixer": dict(common, kv_rank=z["kv_rank"], scale=z["dim"] ** -0.5, mask={"size": z["window"]})}
+    rotary = {"type": "latent_attention_2", "mlp": dense,
+              "mixer": dict(common, kv_rank=z["kv_rank_rot"], rot_dim=z["rot_dim"], scale=(z["dim"] + z["rot_dim"]) ** -0.5,
+                            rot={"base": 500000.0, "dims": z["rot_dim"]})}
+    pattern = [gru, windowed, rotary, gru]
+    return tb.config.PufuzenConfig.from_dict({
+        "architecture": "Pufuzen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+        "logit_scale": 1.0, "layers": [pattern[i % 4] for i in range(z["layers"])]})
+
+
+def run_pufuzen(args):
+    """Prefill (one step of 2,048 tokens) and decoding (batch 1 and `--batch`, 2,048-token contexts) of
+    the Pufuzen design at two widths, beside the Qwen2 decoder of the same width, depth, heads and
+    about the same parameters a layer; then the design's own kernels alone beside the like kernels
+    of the Qwen2 path, each on inputs larger than L2, as bytes a second of the measured copy peak."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    from tokenizer_b200.kernels import ops
+    from tokenizer_b200.parts.model import declared_tensors
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(99)
+    context, steps = 2048, max(8, min(args.steps, 64))
+
+    def timed(fn, reps=1):
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(reps):
+            out = fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / reps, out
+
+    def measure(config, vocab):
+        model = tb.random_model(config, seed=3, dtype="bfloat16", device="cuda:0")
+        params = sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
+        batches = sorted({1, args.batch})
+        engine = tb.engine_for(model, max(batches) * (context + steps + args.warmup + 4 * PAGE), PAGE,
+                               max_requests=max(batches), share_prefixes=False)
+        ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        prefill = []
+        for rep in range(3 + 5):
+            cache = engine.cache.open(("prefill", rep))
+            engine.cache.reserve(cache, PREFILL_TOKENS)
+            entry = StepEntry(cache, ids(PREFILL_TOKENS), [PREFILL_TOKENS - 1])
+            ms, _ = timed(lambda: engine.step([entry]))
+            if rep >= 3:
+                prefill.append(ms)
+            engine.cache.close(cache)
+        out = {"parameters_m": round(params / 1e6, 1), "prefill_ms": sorted(prefill)[len(prefill) // 2]}
+        out["prefill_tok_s"] = PREFILL_TOKENS / (out["prefill_ms"] / 1e3)
+        for batch in batches:
+            caches = [engine.cache.open(("decode", batch, i)) for i in range(batch)]
+            nexts = []
+            for lo in range(0, batch, 4):
+                group = caches[lo:lo + 4]
+                for c in group:
+                    engine.cache.reserve(c, context)
+                logits = engine.step([StepEntry(c, ids(context), [context - 1]) for c in group])
+                nexts += engine.sampler.greedy(logits).tolist()
+            drawn = engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, nexts)], args.warmup)
+            launches = ops.counter.launches
+            ms, _ = timed(lambda: engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, drawn[-1])], steps))
+            out[f"decode_b{batch}_ms"] = ms / steps
+            out[f"decode_b{batch}_tok_s"] = batch * steps / (ms / 1e3)
+            out[f"decode_b{batch}_launches_a_step"] = (ops.counter.launches - launches) // steps
+            for c in caches:
+                engine.cache.close(c)
+        engine.check()
+        del engine, model
+        torch.cuda.empty_cache()
+        return out
+
+    models = {}
+    for name, z in PUFUZEN_SIZES.items():
+        models[name] = {"pufuzen": measure(pufuzen_config(z), z["vocab"])}
+        qwen = tb.Qwen2Config.from_dict(dict(
+            architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=z["layers"],
+            hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=2, head_dim=z["qwen_head_dim"],
+            intermediate_size=z["qwen_inner"], vocab_size=z["vocab"], rope_theta=1000000.0, rms_norm_eps=1e-6,
+            tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False,
+            sliding_window=32768, max_window_layers=z["layers"]))
+        models[name]["qwen2"] = measure(qwen, z["vocab"])
+
+    # ---- kernels alone: inputs larger than L2, a 256 MB write between the timed launches ----
+    dev = "cuda:0"
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def kernel_time(fn, reps=7):
+        times = []
+        for _ in range(3 + reps):
+            flush.zero_()
+            ms, _ = timed(fn)
+            times.append(ms)
+        return sorted(times[3:])[reps // 2]
+
+    kernels = {}
+
+    def record(name, ms, nbytes, like):
+        kernels[name] = {"us": round(ms * 1e3, 1), "gb_s": round(nbytes / (ms / 1e3) / 1e9), "like": like,
+                         "of_measured_copy_peak": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 2)}
+
+    T, W, H, I = 8192, 4096, 2048, 5632
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, device=dev, dtype=torch.float32).to(dtype)
+    proj = rnd(T, 3 * W)
+    state = torch.zeros(4, W, device=dev)
+    out16 = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+    for requests in (1, 4):
+        spans = torch.tensor([T * r // requests for r in range(requests + 1)], dtype=torch.int32, device=dev)
+        slots = torch.arange(requests, dtype=torch.int32, device=dev)
+        record(f"min_gru_scan, {T} tokens of {requests} request(s), width {W}",
+               kernel_time(lambda: ops.min_gru_scan(proj, 0, W, 2 * W, W, state, spans, slots, T // requests, out16)),
+               T * W * (3 * 4 + 2), "silu_gate")
+    z = rnd(T, I + H)
+    act = torch.empty(T, I, dtype=torch.bfloat16, device=dev)
+    coeff = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev)
+    record(f"poly_norm, {T} x {I}", kernel_time(lambda: ops.poly_norm(z[:, :I], coeff, 1e-5, act)), T * I * (4 + 2),
+           "silu_gate")
+    y = rnd(T, H, dtype=torch.bfloat16)
+    delta = torch.empty(T, H, device=dev)
+    record(f"gated_delta, {T} x {H}", kernel_time(lambda: ops.gated_delta(y, None, z[:, I:], delta)), T * H * (2 + 4 + 4),
+           "rms_norm")
+    q_rank, kv_rank, rot = 768, 96, 32
+    wide = rnd(T, q_rank + kv_rank + rot + H)
+    pool = torch.zeros(T + 64, 1, 128, dtype=torch.bfloat16, device=dev)
+    cq = torch.empty(T, q_rank, dtype=torch.bfloat16, device=dev)
+    ones_q, ones_c = torch.ones(q_rank, device=dev), torch.ones(kv_rank, device=dev)
+    freq = torch.tensor([500000.0 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    req = torch.zeros(T, dtype=torch.int32, device=dev)
+    record(f"latent_prepare, {T} tokens", kernel_time(lambda: ops.latent_prepare(
+        wide, 0, q_rank, q_rank, kv_rank, rot, rot, ones_q, ones_c, 1e-5, freq, pos, req, pos, cq, pool)),
+        T * ((q_rank + kv_rank + rot) * 4 + (q_rank + 128) * 2), "rope_store")
+    q = rnd(T, 16 * 128, dtype=torch.bfloat16)
+    record(f"rotate_interleaved, {T} tokens x 16 heads, 32 of 128 lanes",
+           kernel_time(lambda: ops.rotate_interleaved(q, 16, kv_rank, rot, freq, pos, req)), T * 16 * 128 * 2 * 2 // 2,
+           "rope_store")
+    # the like kernels of the Qwen2 path
+    gu = rnd(T, 2 * I, dtype=torch.bfloat16)
+    record(f"silu_gate, {T} x {I} (Qwen2 path)", kernel_time(lambda: ops.silu_gate(gu, act)), T * I * 6, None)
+    x = rnd(T, H)
+    gain = torch.ones(H, device=dev)
+    h16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    record(f"rms_norm with pending add, {T} x {H} (Qwen2 path)",
+           kernel_time(lambda: ops.rms_norm(x, gain, 1e-6, h16, delta=y)), T * H * (4 + 4 + 2 + 2), None)
+    nh, nkv, d = 16, 2, 128
+    qkv = rnd(T, (nh + 2 * nkv) * d, dtype=torch.bfloat16)
+    cos, sin = ops.rope_table(torch.tensor([1e6 ** (-2.0 * i / d) for i in range(d // 2)], device=dev), T)
+    q_out = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+    k_pool = torch.zeros(T + 64, nkv, d, dtype=torch.bfloat16, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    record(f"rope_store, {T} tokens (Qwen2 path)", kernel_time(lambda: ops.rope_store(
+        qkv, None, pos, pos, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, d)), T * (nh + 2 * nkv) * d * 2 * 2, None)
+    # decoding attention: 64 rows of 8,192 keys; the latent's row is read as keys and as values
+    rows, keys = 64, 8192
+    pages = rows * keys // PAGE
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(rows, keys // PAGE)
+    row_req = torch.arange(rows, dtype=torch.int32, device=dev)
+    last = torch.full((rows,), keys - 1, dtype=torch.int32, device=dev)
+    lat = rnd(rows * keys, 1, 128, dtype=torch.bfloat16)
+    ql = rnd(rows, 16 * 128, dtype=torch.bfloat16)
+    ol = torch.empty_like(ql)
+    sink = torch.zeros(16, device=dev)
+    record("decode attention over a cached latent, 64 rows x 8,192 keys, 16 heads, rows of 128 lanes",
+           kernel_time(lambda: ops.decode_attention(ql, lat, lat, ol, table, row_req, last, 16, 1, 128, PAGE, None, 0.09,
+                                                    sink=sink)), rows * keys * 128 * 2, "decode attention (Qwen2 path)")
+    kq, vq = rnd(rows * keys, 2, 128, dtype=torch.bfloat16), rnd(rows * keys, 2, 128, dtype=torch.bfloat16)
+    record("decode attention, 64 rows x 8,192 keys, 16 heads over 2 of 128 lanes (Qwen2 path)",
+           kernel_time(lambda: ops.decode_attention(ql, kq, vq, ol, table, row_req, last, 16, 2, 128, PAGE, None, 0.09)),
+           rows * keys * 2 * 2 * 128 * 2, None)
+    ops.raise_if_error()
+    print(json.dumps({
+        "metric": "prefill and decode tok/s of the Pufuzen design beside Qwen2 at equal width, depth and parameters",
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
+        "data": "synthetic: random weights drawn on the device, uniform random token ids",
+        "config": {"sizes": PUFUZEN_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
+                   "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
+        "models": models, "kernels": kernels}))
     return 0
 
 
