@@ -51,6 +51,7 @@ def recurrence_reference(zp, u, g, state):
 def test_min_gru_scan_carries_each_request_its_own_state(width, lengths, out_dtype):
     total, extra = sum(lengths), 11                       # the three ranges lie inside a wider product
     proj = rnd(total, 3 * width + extra, seed=1, scale=2.0)
+    bias = rnd(3 * width + extra, seed=12)                # the product's bias is added by the kernel
     slots = [3, 0, 5, 1][:len(lengths)]
     state = rnd(6, width, seed=2)
     before = state.clone()
@@ -72,9 +73,9 @@ def test_min_gru_scan_carries_each_request_its_own_state(width, lengths, out_dty
         sub_out = torch.empty(len(rows), width, dtype=out_dtype, device=DEV)
         longest = max(b - a for a, b in zip(spans, spans[1:]))
         ops().min_gru_scan(sub, extra, extra + width, extra + 2 * width, width, state,
-                           torch.tensor(spans, dtype=torch.int32, device=DEV), slot_t, longest, sub_out)
+                           torch.tensor(spans, dtype=torch.int32, device=DEV), slot_t, longest, sub_out, bias=bias)
         out[torch.tensor(rows, device=DEV)] = sub_out
-    p = proj.double().cpu()
+    p = proj.double().cpu() + bias.double().cpu()
     for r, n in enumerate(lengths):
         rows = slice(starts[r], starts[r + 1])
         want, end = recurrence_reference(p[rows, extra:extra + width], p[rows, extra + width:extra + 2 * width],
@@ -85,7 +86,8 @@ def test_min_gru_scan_carries_each_request_its_own_state(width, lengths, out_dty
     assert torch.equal(state[untouched], before[untouched])
     # the same in one call
     state2, out2 = before.clone(), torch.empty_like(out)
-    ops().min_gru_scan(proj, extra, extra + width, extra + 2 * width, width, state2, q_start, slot_t, max(lengths), out2)
+    ops().min_gru_scan(proj, extra, extra + width, extra + 2 * width, width, state2, q_start, slot_t, max(lengths), out2,
+                       bias=bias)
     close(out2, out, out_dtype, "one call against two")
     close(state2, state, torch.float32)
 
@@ -97,8 +99,9 @@ def test_poly_norm(dtype, n):
     wide = rnd(9, n + 40, seed=3, scale=1.5)
     coeff = torch.tensor([0.7, -0.3, 0.2, 0.05], device=DEV)
     out = torch.empty(9, n, dtype=dtype, device=DEV)
-    ops().poly_norm(wide[:, :n], coeff, 1e-5, out)
-    z = wide[:, :n].double().cpu()
+    bias = rnd(n + 40, seed=13)
+    ops().poly_norm(wide[:, :n], coeff, 1e-5, out, bias=bias[:n])
+    z = wide[:, :n].double().cpu() + bias[:n].double().cpu()
     norm = lambda v: v / torch.sqrt((v * v).mean(-1, keepdim=True) + 1e-5)
     close(out, 0.7 * norm(z) - 0.3 * norm(z * z) + 0.2 * norm(z ** 3) + 0.05, dtype)
 
@@ -115,6 +118,16 @@ def test_gated_delta_takes_a_product_whole_or_in_partial_sums():
     parts, bias = rnd(3, rows, hidden, seed=6), rnd(hidden, seed=7)
     ops().gated_delta(parts, bias, pre, out)
     close(out, (parts.double().cpu().sum(0) + bias.double().cpu()) * gate, torch.float32)
+    # the gate's own bias; lanes that 16-byte loads do not fit (a width of 50, a slice that starts at lane 30)
+    pre_bias = rnd(hidden + 1, seed=14)[1:]
+    ops().gated_delta(parts, bias, pre, out, pre_bias=pre_bias)
+    gate = torch.sigmoid(pre.double().cpu() + pre_bias.double().cpu())
+    close(out, (parts.double().cpu().sum(0) + bias.double().cpu()) * gate, torch.float32)
+    wide_pre, wide_bias = rnd(rows, 64 + 32, seed=15), rnd(64, seed=16)
+    y64, out64 = rnd(rows, 64, seed=17, dtype=torch.bfloat16), torch.empty(rows, 64, device=DEV)
+    ops().gated_delta(y64, None, wide_pre[:, 32:], out64, pre_bias=wide_bias)
+    close(out64, y64.double().cpu() * torch.sigmoid(wide_pre[:, 32:].double().cpu() + wide_bias.double().cpu()),
+          torch.float32)
 
 
 # ---- the kernels around the cached latent -------------------------------------------------------------

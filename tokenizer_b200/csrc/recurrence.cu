@@ -10,29 +10,37 @@
 // the product with silu(g) are 32-bit whatever the type of the projection's output.
 //
 // A step's rows of one request are taken in runs of TY * K tokens: thread (x, y) of a block owns
-// channel x of the block's 32 and K consecutive tokens; it folds them into one affine map
+// one of the block's channels and K consecutive tokens; it folds them into one affine map
 // S -> P S + B, the maps of the block's TY threads of a channel are chained through shared
 // memory, and every thread then walks its K tokens again from the state it was handed, out of
-// registers.  Every input is read once.  A step of single tokens runs with TY = 1, K = 1.
+// registers.  Every input is read once.  A block owns 32 channels (128 bytes of every row) and
+// 8 runs where channels and requests give several blocks a multiprocessor, 32 runs where a lone
+// long prompt leaves few blocks, which must then keep many loads in flight each.  A step of
+// single tokens runs one thread a channel.
 #include "common.cuh"
 
-#define REC_CHANNELS 32
+#define REC_MAX_X 32
 #define REC_MAX_TY 32
 
 __device__ __forceinline__ float rec_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 template <typename TI, typename TO, int K>
-__global__ void __launch_bounds__(REC_CHANNELS * REC_MAX_TY)
-min_gru_scan_kernel(const TI* __restrict__ proj, int ld, int z_at, int u_at, int g_at, int width,
+__global__ void __launch_bounds__(REC_MAX_X * REC_MAX_TY)
+min_gru_scan_kernel(const TI* __restrict__ proj, const float* __restrict__ bias, int ld, int z_at, int u_at,
+                    int g_at, int width,
                     float* __restrict__ state, const int* __restrict__ q_start,
                     const int* __restrict__ state_slot, TO* __restrict__ out) {
-  __shared__ float p_s[REC_MAX_TY][REC_CHANNELS + 1];
-  __shared__ float b_s[REC_MAX_TY][REC_CHANNELS + 1];
-  __shared__ float carry_s[REC_CHANNELS];
+  __shared__ float p_s[REC_MAX_TY][REC_MAX_X + 1];
+  __shared__ float b_s[REC_MAX_TY][REC_MAX_X + 1];
+  __shared__ float carry_s[REC_MAX_X];
   const int x = threadIdx.x, y = threadIdx.y, ty = blockDim.y;
-  const int c = blockIdx.x * REC_CHANNELS + x;
+  const int c = blockIdx.x * blockDim.x + x;
   const int r = blockIdx.y;
   const bool live = c < width;
+  // the projection's biases (one float32 a column of the product, or none): weights, read before the wait
+  const float bz = (bias && live) ? bias[z_at + c] : 0.f;
+  const float bu = (bias && live) ? bias[u_at + c] : 0.f;
+  const float bg = (bias && live) ? bias[g_at + c] : 0.f;
   // the spans and slots were written before the predecessor started
   const int first = q_start[r], last = q_start[r + 1];
   const int slot = state_slot[r];
@@ -50,9 +58,9 @@ min_gru_scan_kernel(const TI* __restrict__ proj, int ld, int z_at, int u_at, int
       const int t = mine + k;
       if (live && t < last) {
         const TI* row = proj + (size_t)t * ld;
-        const float z = rec_sigmoid(to_float(row[z_at + c]));
-        const float u = to_float(row[u_at + c]);
-        const float g = to_float(row[g_at + c]);
+        const float z = rec_sigmoid(to_float(row[z_at + c]) + bz);
+        const float u = to_float(row[u_at + c]) + bu;
+        const float g = to_float(row[g_at + c]) + bg;
         const float cand = u >= 0.f ? u + 0.5f : rec_sigmoid(u);
         a[k] = 1.0f - z;
         b[k] = z * cand;
@@ -86,23 +94,30 @@ min_gru_scan_kernel(const TI* __restrict__ proj, int ld, int z_at, int u_at, int
 // proj: [rows, ld] (float32 or bfloat16) with the three column ranges starting at z_at, u_at,
 // g_at, each `width` wide; out: [rows, width] dense.  `longest`: the most rows a request brings
 // to the step (chooses the shape of a block).
-TOKB200_API int tokb200_min_gru_scan(const void* proj, int proj_dtype, int ld, int z_at, int u_at,
+TOKB200_API int tokb200_min_gru_scan(const void* proj, int proj_dtype, const float* bias, int ld, int z_at, int u_at,
                                      int g_at, int width, float* state, const int* q_start,
                                      const int* state_slot, int n_requests, int longest, void* out,
                                      int out_dtype, cudaStream_t stream) {
   if (n_requests <= 0 || longest <= 0) return TOKB200_OK;
   if (width <= 0 || ld < width || n_requests > 65535) return TOKB200_BAD_SIZE;
-  dim3 grid((width + REC_CHANNELS - 1) / REC_CHANNELS, n_requests);
-  int ty = 1;
-  while (ty < REC_MAX_TY && ty * 4 < longest) ty *= 2;
   const bool single = longest == 1;
-  dim3 block(REC_CHANNELS, single ? 1 : ty);
+  // a block owns 32 channels (128 bytes of every row).  Where channels and requests give two blocks
+  // a multiprocessor and more, 8 runs (256 threads, several blocks a multiprocessor); else 32 runs
+  // (1,024 threads), so that the few blocks of a lone long prompt keep enough loads in flight
+  const int cx = REC_MAX_X;
+  int ty = 1;
+  if (!single) {
+    ty = (long long)((width + 31) / 32) * n_requests >= 2 * 148 ? 8 : REC_MAX_TY;
+    while (ty > 1 && (ty / 2) * 8 >= longest) ty /= 2;     // no more runs than the longest request fills
+  }
+  dim3 grid((width + cx - 1) / cx, n_requests);
+  dim3 block(cx, ty);
 #define LAUNCH(TI, TO)                                                                              \
   return single ? launch_dependent(min_gru_scan_kernel<TI, TO, 1>, grid, block, 0, stream,         \
-                                   (const TI*)proj, ld, z_at, u_at, g_at, width, state, q_start,  \
+                                   (const TI*)proj, bias, ld, z_at, u_at, g_at, width, state, q_start,  \
                                    state_slot, (TO*)out)                                            \
-                : launch_dependent(min_gru_scan_kernel<TI, TO, 4>, grid, block, 0, stream,         \
-                                   (const TI*)proj, ld, z_at, u_at, g_at, width, state, q_start,  \
+                : launch_dependent(min_gru_scan_kernel<TI, TO, 8>, grid, block, 0, stream,         \
+                                   (const TI*)proj, bias, ld, z_at, u_at, g_at, width, state, q_start,  \
                                    state_slot, (TO*)out)
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);

@@ -1009,41 +1009,48 @@ def _sliced_ptr(t: torch.Tensor):
 
 
 def min_gru_scan(proj: torch.Tensor, z_at: int, u_at: int, g_at: int, width: int, state: torch.Tensor,
-                 q_start: torch.Tensor, state_slot: torch.Tensor, longest: int, out: torch.Tensor) -> None:
+                 q_start: torch.Tensor, state_slot: torch.Tensor, longest: int, out: torch.Tensor,
+                 bias: Optional[torch.Tensor] = None) -> None:
     """The minGRU recurrence over a step's rows (see csrc/recurrence.cu).  `proj` [T, N] holds the
-    three pre-activations in column ranges starting at z_at, u_at, g_at; `state` float32
-    [slots, width] is read and written in place; `out` [T, width] dense."""
+    three pre-activations in column ranges starting at z_at, u_at, g_at (`bias`, float32 [N]: the
+    product's bias, added here); `state` float32 [slots, width] is read and written in place; `out`
+    [T, width] dense."""
     if state.dtype != torch.float32 or state.shape[-1] != width or tuple(out.shape) != (proj.shape[0], width):
         raise ValueError("min_gru_scan: state is float32 [slots, width], out [T, width]")
-    if max(z_at, u_at, g_at) + width > proj.shape[1]:
-        raise ValueError("min_gru_scan: the column ranges leave the projection")
+    if max(z_at, u_at, g_at) + width > proj.shape[1] or (bias is not None and (
+            bias.dtype != torch.float32 or bias.numel() < max(z_at, u_at, g_at) + width)):
+        raise ValueError("min_gru_scan: the column ranges leave the projection (or its bias)")
     _check(_lib("recurrence").tokb200_min_gru_scan(
-        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(z_at), _i(u_at), _i(g_at), _i(width), _ptr(state),
+        _sliced_ptr(proj), _i(_tag(proj)), _ptr(bias), _i(_ld(proj)), _i(z_at), _i(u_at), _i(g_at), _i(width), _ptr(state),
         _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _i(longest), _ptr(out), _i(_tag(out)),
         _stream()), "min_gru_scan")
 
 
-def poly_norm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out: torch.Tensor) -> None:
-    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps); `coeff`
-    float32 [4] = (a, b, c, e) on the device; `z` may be a column slice of a wider matrix."""
+def poly_norm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out: torch.Tensor,
+              bias: Optional[torch.Tensor] = None) -> None:
+    """out = a N(v) + b N(v^2) + c N(v^3) + e per row, v = z (+ bias, float32 [n]), N(v) = v /
+    sqrt(mean(v^2) + eps); `coeff` float32 [4] = (a, b, c, e) on the device; `z` may be a column
+    slice of a wider matrix."""
     n_rows, n = z.shape
-    if coeff.dtype != torch.float32 or coeff.numel() != 4 or tuple(out.shape) != (n_rows, n):
-        raise ValueError("poly_norm: four float32 numbers, out of z's shape")
+    if coeff.dtype != torch.float32 or coeff.numel() != 4 or tuple(out.shape) != (n_rows, n) or \
+            (bias is not None and (bias.dtype != torch.float32 or bias.numel() != n)):
+        raise ValueError("poly_norm: four float32 numbers, out of z's shape, a float32 bias of z's width")
     _check(_lib("activation").tokb200_poly_norm(
-        _sliced_ptr(z), _i(_tag(z)), _i(_ld(z)), _ptr(coeff), _ptr(out), _i(_tag(out)), _i(n_rows), _i(n),
+        _sliced_ptr(z), _i(_tag(z)), _sliced_ptr(bias) if bias is not None else _ptr(None), _i(_ld(z)), _ptr(coeff), _ptr(out), _i(_tag(out)), _i(n_rows), _i(n),
         _f(eps), _stream()), "poly_norm")
 
 
-def gated_delta(y: torch.Tensor, bias: Optional[torch.Tensor], pre: torch.Tensor, out: torch.Tensor) -> None:
-    """out (float32 [T, H]) = (y + bias) * sigmoid(pre): `y` is [T, H] or float32 partial sums
-    [S, T, H]; `pre` [T, H] may be a column slice of a wider matrix."""
+def gated_delta(y: torch.Tensor, bias: Optional[torch.Tensor], pre: torch.Tensor, out: torch.Tensor,
+                pre_bias: Optional[torch.Tensor] = None) -> None:
+    """out (float32 [T, H]) = (y + bias) * sigmoid(pre + pre_bias): `y` is [T, H] or float32 partial
+    sums [S, T, H]; `pre` [T, H] may be a column slice of a wider matrix; the biases are float32 [H]."""
     n_rows, hidden = out.shape
     if out.dtype != torch.float32 or tuple(pre.shape) != (n_rows, hidden):
         raise ValueError("gated_delta: out is float32 [T, H], the gate's pre-activation [T, H]")
     n_partials, stride = _partials(y, out)
     _check(_lib("activation").tokb200_gated_delta(
         _ptr(y), _i(_tag(y)), _i(n_partials), _ll(stride), _ptr(bias), _sliced_ptr(pre), _i(_tag(pre)),
-        _i(_ld(pre)), _ptr(out), _i(n_rows), _i(hidden), _stream()), "gated_delta")
+        _sliced_ptr(pre_bias) if pre_bias is not None else _ptr(None), _i(_ld(pre)), _ptr(out), _i(n_rows), _i(hidden), _stream()), "gated_delta")
 
 
 def latent_prepare(proj: torch.Tensor, q_at: int, q_rank: int, c_at: int, kv_rank: int, rot_dim: int,

@@ -109,9 +109,11 @@ class GatedPreNormResidual:
         return out
 
     def _gated(self, stream, part, gate, h, y):
-        pre = part.side_pre if id(part) in self._carried else gate.forward(h)
+        carried = id(part) in self._carried
+        pre = part.side_pre if carried else gate.forward(h)
         delta = torch.empty(stream.x.shape, dtype=torch.float32, device=stream.x.device)
-        ops.gated_delta(y, getattr(part, "deferred_bias", None), pre, delta)
+        ops.gated_delta(y, getattr(part, "deferred_bias", None), pre, delta,
+                        pre_bias=part.side_bias if carried else None)
         stream.add(delta)
 
     def forward(self, stream, ctx, cache):

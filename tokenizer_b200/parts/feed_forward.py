@@ -140,7 +140,8 @@ class PolyNormMLP(SideProjection):
     def forward(self, h):
         z = self.up.forward(h, out_dtype=torch.float32)
         act = self.runtime.empty(h.shape[0], self.inner)
-        ops.poly_norm(z[:, :self.inner], self.coeff, self.eps, act)
+        ops.poly_norm(z[:, :self.inner], self.coeff, self.eps, act,
+                      bias=self.stack_bias[:self.inner] if self.stack_bias is not None else None)
         self._keep_side(z)
         if self.deferred_bias is not None:
             return self.down.forward(act, use_bias=False, partials_ok=True)

@@ -20,25 +20,32 @@ from .linear import Linear
 class SideProjection:
     """Mixers and feed-forwards whose first step is a product of their input may carry one more
     projection of the same input in that product (`take_side(weight, bias)`, CPU tensors as
-    stored): its result of the last `forward` is `side_pre` [T, rows of weight], float32.  The
-    arrangement of a layer uses it for a gate on the sublayer's output."""
+    stored): its result of the last `forward` is `side_pre` [T, rows of weight], float32, still
+    lacking `side_bias`.  The arrangement of a layer uses it for a gate on the sublayer's output.
+    The stacked product is computed WITHOUT its biases: `stack_bias` (float32, one a column, or
+    None) is added by the kernels that consume the columns, which spares a pass over the product."""
 
     side_rows = 0
     side_pre = None
+    side_bias = None
+    stack_bias = None
 
     def _stack(self, runtime, weights, biases, side):
         """One Linear over `weights` stacked row-wise (+ the side projection); `biases` are
         per-weight float tensors or None (zeros)."""
+        self.side_rows = 0
         if side is not None:
             weights, biases = weights + [side[0]], biases + [side[1]]
             self.side_rows = side[0].shape[0]
         self.own_rows = sum(w.shape[0] for w in weights) - self.side_rows
-        bias = None
+        self.stack_bias = self.side_bias = None
         if any(b is not None for b in biases):
             bias = torch.cat([torch.zeros(w.shape[0], dtype=torch.float32, device=w.device) if b is None
                               else b.to(torch.float32) for w, b in zip(weights, biases)])
-            bias = runtime.vector(bias)
-        return Linear(runtime.matrix(torch.cat(weights, dim=0)), bias)
+            self.stack_bias = runtime.vector(bias)
+            if self.side_rows and biases[-1] is not None:
+                self.side_bias = self.stack_bias[self.own_rows:]
+        return Linear(runtime.matrix(torch.cat(weights, dim=0)))
 
     def _keep_side(self, product):
         self.side_pre = product[:, self.own_rows:] if self.side_rows else None
@@ -81,7 +88,7 @@ class MinGRU(SideProjection):
         product = self.inputs.forward(h, out_dtype=torch.float32)
         y = self.runtime.empty(ctx.n_tokens, w)
         ops.min_gru_scan(product, 0, w, 2 * w, w, cache.state, ctx.q_start, ctx.state_slot,
-                         max(ctx.max_q_len, 1), y)
+                         max(ctx.max_q_len, 1), y, bias=self.stack_bias)
         self._keep_side(product)
         return self.out.forward(y, partials_ok=True)
 
