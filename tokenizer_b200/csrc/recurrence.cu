@@ -22,7 +22,16 @@
 #define REC_MAX_X 32
 #define REC_MAX_TY 32
 
-__device__ __forceinline__ float rec_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+// FAST (where the outputs are bfloat16): the exponential and the division by the hardware's
+// approximations, exact to about 2 ulp of float32, far below the output's rounding; the float32
+// path keeps the library's expf and the IEEE division.  Three sigmoids a token and channel make
+// this kernel bound by them otherwise (8,192 tokens x 4,096 channels: 290 us against 72 us for
+// its bytes).
+template <bool FAST>
+__device__ __forceinline__ float rec_sigmoid(float v) {
+  if (FAST) return __fdividef(1.0f, 1.0f + __expf(-v));
+  return 1.0f / (1.0f + expf(-v));
+}
 
 template <typename TI, typename TO, int K>
 __global__ void __launch_bounds__(REC_MAX_X * REC_MAX_TY)
@@ -33,6 +42,7 @@ min_gru_scan_kernel(const TI* __restrict__ proj, const float* __restrict__ bias,
   __shared__ float p_s[REC_MAX_TY][REC_MAX_X + 1];
   __shared__ float b_s[REC_MAX_TY][REC_MAX_X + 1];
   __shared__ float carry_s[REC_MAX_X];
+  constexpr bool FAST = sizeof(TO) == 2;
   const int x = threadIdx.x, y = threadIdx.y, ty = blockDim.y;
   const int c = blockIdx.x * blockDim.x + x;
   const int r = blockIdx.y;
@@ -58,13 +68,13 @@ min_gru_scan_kernel(const TI* __restrict__ proj, const float* __restrict__ bias,
       const int t = mine + k;
       if (live && t < last) {
         const TI* row = proj + (size_t)t * ld;
-        const float z = rec_sigmoid(to_float(row[z_at + c]) + bz);
+        const float z = rec_sigmoid<FAST>(to_float(row[z_at + c]) + bz);
         const float u = to_float(row[u_at + c]) + bu;
         const float g = to_float(row[g_at + c]) + bg;
-        const float cand = u >= 0.f ? u + 0.5f : rec_sigmoid(u);
+        const float cand = u >= 0.f ? u + 0.5f : rec_sigmoid<FAST>(u);
         a[k] = 1.0f - z;
         b[k] = z * cand;
-        gate[k] = g * rec_sigmoid(g);
+        gate[k] = g * rec_sigmoid<FAST>(g);
       } else {
         a[k] = 1.f; b[k] = 0.f; gate[k] = 0.f;
       }
