@@ -47,6 +47,7 @@ def test_the_architecture_is_chosen_by_its_name_and_every_size_comes_from_the_fi
     (lambda r: r["layers"][2]["mixer"]["rot"].update(dims=3), "rot.dims"),
     (lambda r: r.pop("logit_scale"), "logit_scale"),
     (lambda r: r["layers"][1]["mixer"]["mask"].update(size=0), "size"),
+    (lambda r: r["layers"][1]["mixer"].update(mask=7), "mask"),
 ])
 def test_a_configuration_that_cannot_be_a_model_is_refused(spoil, word):
     r = raw([gru(40), windowed(3, 8, 6, 10, 12, 5, 0.3, ff=30), rotary(2, 8, 4, 6, 10, 12, 99.0, 0.2)])

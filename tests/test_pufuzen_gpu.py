@@ -259,7 +259,8 @@ def test_a_sink_and_values_that_are_the_key_rows_in_every_attention_kernel(kerne
 
 
 # ---- whole models -----------------------------------------------------------------------------------
-LENGTHS = {"p": [1, 2, 23, 100, 131, 64], "q": [5, 19, 97, 140, 260, 33], "r": [3, 40, 130, 64, 17, 90]}
+LENGTHS = {"p": [1, 2, 23, 100, 131, 64], "q": [5, 19, 97, 140, 260, 33], "r": [3, 40, 130, 64, 17, 90],
+           "s": [1, 9, 70, 129, 30, 2], "t": [2, 50, 140, 7, 33]}
 
 
 @pytest.fixture(scope="module", params=sorted(TINY))

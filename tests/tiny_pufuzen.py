@@ -52,7 +52,19 @@ def tiny_r():
                    windowed(2, 16, 20, 12, 40, 100, 0.25)], vocab=130, width=40, eps=3e-6, logit_scale=1.0), 5, 32
 
 
-TINY = {"p": tiny_p, "q": tiny_q, "r": tiny_r}
+def tiny_s():
+    """Sizes that no vector load fits (a width of 50, a vocabulary of 77, latents of 10 and 18 lanes, one
+    head), a window longer than any request, a window of two keys, pages of 64."""
+    return config([rotary(1, 10, 6, 6, 10, 18, 1000.0, 0.3), gru(33, ff=30), windowed(1, 6, 10, 14, 18, 500, 0.4, ff=26),
+                   windowed(3, 10, 6, 10, 12, 2, 0.3)], vocab=77, width=50, eps=1e-5, logit_scale=2.0), 6, 64
+
+
+def tiny_t():
+    """Recurrent layers alone: a model that keeps no keys at all."""
+    return config([gru(48, ff=64), gru(96), gru(32, ff=40)], vocab=200, width=32, eps=1e-6, logit_scale=1.5), 7, 16
+
+
+TINY = {"p": tiny_p, "q": tiny_q, "r": tiny_r, "s": tiny_s, "t": tiny_t}
 # sharper attention and larger sinks, so that a key seen or missed moves the logits in bfloat16 too
 SHARPEN = {r"mix\.uq$": 6.0, r"mix\.sink$": 2.0, r"^embed$|^head$": 5.0}
 

@@ -7,7 +7,8 @@ config.json keys: `architecture` ("Pufuzen"), `vocab`, `width`, `logit_scale`, `
 `layers`: a list of {`type`, `mixer` (the mixer's sizes), `mlp` (null or {`kind`: "dense", `ff`})}.
   type "mingru":              mixer {width}
   type "latent_attention":    mixer {heads, dim, vdim, q_rank, kv_rank, scale, mask {size}}
-                              (no positions; a query sees itself and the mask.size - 1 keys before)
+                              (no positions; a query sees itself and the mask.size - 1 keys before;
+                              a mixer without `mask` sees every earlier key)
   type "latent_attention_2":  mixer {heads, dim, rot_dim, vdim, q_rank, kv_rank, scale,
                               rot {base, dims}} (causal; rotary lanes; a sink per head)
 Tensors: `embed`, `l<i>.norm1`, `l<i>.norm2`, `l<i>.mix.*`, `l<i>.mlp.*`, `l<i>.rg1`, `l<i>.rg2`
@@ -28,7 +29,7 @@ POSITIONS = 1 << 20
 
 _MIXER_KEYS = {
     "mingru": ["width"],
-    "latent_attention": ["heads", "dim", "vdim", "q_rank", "kv_rank", "scale", "mask"],
+    "latent_attention": ["heads", "dim", "vdim", "q_rank", "kv_rank", "scale"],
     "latent_attention_2": ["heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "scale", "rot"],
 }
 
@@ -68,7 +69,7 @@ class PufuzenConfig:
                 as_int(m, key, 1)
         if kind != "mingru":
             as_float(m, "scale")
-        if kind == "latent_attention":
+        if kind != "mingru" and m.get("mask") is not None:      # no mask: every earlier key is seen
             if not isinstance(m["mask"], dict) or "size" not in m["mask"]:
                 raise ConfigError(f"{what}: mask must be an object with size")
             as_int(m["mask"], "size", 1)
@@ -102,11 +103,12 @@ class PufuzenConfig:
             return PartSpec("min_gru", {"hidden_size": self.width, "width": m["width"]}, prefix)
         params = {"hidden_size": self.width, "heads": m["heads"], "dim": m["dim"], "vdim": m["vdim"],
                   "q_rank": m["q_rank"], "kv_rank": m["kv_rank"], "scale": float(m["scale"]), "eps": self.eps}
+        # a query sees itself and the mask.size - 1 keys before it
+        window = int(m["mask"]["size"]) - 1 if m.get("mask") is not None else None
         if layer["type"] == "latent_attention":
-            # a query sees itself and the mask.size - 1 keys before it
-            params.update(rot_dim=0, window=int(m["mask"]["size"]) - 1, sink=False, position=None)
+            params.update(rot_dim=0, window=window, sink=False, position=None)
         else:
-            params.update(rot_dim=m["rot_dim"], window=None, sink=True,
+            params.update(rot_dim=m["rot_dim"], window=window, sink=True,
                           position=PartSpec("rope_interleaved", {"base": float(m["rot"]["base"]),
                                                                  "dims": int(m["rot"]["dims"])}))
         return PartSpec("latent_attention", params, prefix)
