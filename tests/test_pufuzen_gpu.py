@@ -408,3 +408,29 @@ def test_long_decoding_on_the_device(model, dtype):
             assert tokens == plain.greedy_generate(raw, w, prompt, 301)
         else:
             near_best(raw, w, prompt, tokens, dtype)
+
+
+def test_the_command_line_generates_from_a_configuration_of_this_design(tmp_path):
+    """`--random-weights config.json` draws the weights the configuration declares; two prompts go
+    through the scheduler and print the ids each gets from the plain implementation."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import tokenizer_b200 as tb
+    cfg, seed, page = TINY["p"]()
+    path = str(tmp_path / "config.json")
+    with open(path, "w") as fh:
+        json.dump(cfg.to_dict(), fh)
+    folder = tb.write_random_model(str(tmp_path / "same"), cfg, 0)        # the command line's default seed
+    raw, w = plain.load_folder(folder)
+    prompts = [random_ids(11, cfg.vocab, 801), random_ids(40, cfg.vocab, 802)]
+    cli = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "qwen-infer")
+    args = [sys.executable, cli, "--random-weights", path, "--weights-seed", "0", "--dtype", "float32",
+            "--max-tokens", "10", "--page-size", str(page)]
+    for prompt in prompts:
+        args += ["--ids", ",".join(str(t) for t in prompt)]
+    proc = subprocess.run(args, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    want = [" ".join(str(t) for t in plain.greedy_generate(raw, w, prompt, 10)) for prompt in prompts]
+    assert proc.stdout.strip().splitlines() == want

@@ -102,7 +102,12 @@ __device__ __forceinline__ float dec_peer_load(const float* local, unsigned rank
 // counter.
 // EARLY: the warps' first tiles are asked for before the wait on the predecessor (short pieces,
 // where a trip to memory is a good part of the kernel's time; in a long piece it only costs registers).
-template <bool CLUSTER, bool EARLY>
+// ALIAS: the values are the key rows themselves (`v_pool` is `k_pool`: a cache that keeps one row a
+// token, read as both).  A tile's rows are then fetched once, into the staging buffer, and the key
+// fragments are read from there instead of from global memory: the wait for the tile's rows moves
+// ahead of the scores (the rows were asked for one tile earlier, so they have had a whole tile's
+// time to land).
+template <bool CLUSTER, bool EARLY, bool ALIAS>
 __global__ void __launch_bounds__(DEC_THREADS, HEAD_DIM <= 64 ? 2 : 1)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
@@ -213,7 +218,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   if (early) {
     slots_now = tile_slots(k_mine);
     if (kVBuffers == 2) stage_values(slots_now, v_buf);
-    load_keys(slots_now);
+    if (!ALIAS) load_keys(slots_now);
   }
   pdl_wait();
   pdl_launch();
@@ -254,7 +259,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   if (have_tile && !early) {
     slots_now = tile_slots(k_mine);
     if (kVBuffers == 2) stage_values(slots_now, v_buf);
-    load_keys(slots_now);
+    if (!ALIAS) load_keys(slots_now);
   }
   for (int k0 = first + warp * DEC_TILE; k0 <= last; k0 += DEC_BLOCK_KEYS, turn ^= 1) {
     __nv_bfloat16* v_s = v_buf + (size_t)(kVBuffers == 2 ? turn : 0) * DEC_TILE * kVStride;
@@ -263,6 +268,19 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     if (kVBuffers == 1) stage_values(slots_now, v_s);   // the last tile's sum is done (the __syncwarp below)
     else if (more) stage_values(slots_next, v_buf + (size_t)(turn ^ 1) * DEC_TILE * kVStride);
     slots_now = slots_next;
+    if (ALIAS) {
+      // this tile's rows have landed (the next tile's may not); the key fragments come from them
+      if (kVBuffers == 2 && more) asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      __syncwarp();
+#pragma unroll
+      for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+        const __nv_bfloat16* krow = v_s + (nt * 8 + g) * kVStride;
+#pragma unroll
+        for (int st = 0; st < kSteps32; ++st) kf[nt][st] = *reinterpret_cast<const uint4*>(krow + dec_k_offset(st, t));
+        if (kTail16) kt[nt] = *reinterpret_cast<const uint2*>(krow + kSteps32 * 32 + 4 * t);
+      }
+    }
     float s[DEC_TILE / 8][4];
 #pragma unroll
     for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
@@ -274,7 +292,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       }
       if (kTail16) dec_mma(s[nt], qt, kt[nt].x, kt[nt].y);
     }
-    if (more) load_keys(slots_next);
+    if (!ALIAS && more) load_keys(slots_next);
     // ---- scale, mask, running softmax: rows g (heads 0..7) and g + 8 (heads 8..15) ----
     float m_new[2] = {m_run[0], m_run[1]};
     if (k0 + DEC_TILE - 1 <= last) {          // a whole tile (every tile of a piece but its last): no key to mask
@@ -325,9 +343,11 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       o[i][0] *= corr[0]; o[i][1] *= corr[0];
       o[i][2] *= corr[1]; o[i][3] *= corr[1];
     }
-    if (kVBuffers == 2 && more) asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this tile's values have landed (the next tile's may not)
-    else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    __syncwarp();
+    if (!ALIAS) {
+      if (kVBuffers == 2 && more) asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this tile's values have landed (the next tile's may not)
+      else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      __syncwarp();
+    }
     // ---- o += p v ----
 #pragma unroll
     for (int ks = 0; ks < DEC_TILE / 16; ++ks) {
@@ -509,8 +529,8 @@ TOKB200_API int tokb200_decode_attention(
       int device = 0, sms = 148, per_sm = 0;
       if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
       if (smem > 48 * 1024)
-        cudaFuncSetAttribute(decode_attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<false, false>, DEC_THREADS, smem) !=
+        cudaFuncSetAttribute(decode_attention_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<false, false, false>, DEC_THREADS, smem) !=
               cudaSuccess || per_sm < 1)
         per_sm = 1;
       have = per_sm * sms;
@@ -547,19 +567,23 @@ TOKB200_API int tokb200_decode_attention(
   const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX && pairs * most <= slots;
   // pieces of up to two passes: the first tiles before the wait (see EARLY)
   const bool early = min_chunk <= 2 * DEC_BLOCK_KEYS;
+  // one pool read as keys and as values, while a warp has two staging buffers (see ALIAS)
+  const bool alias = k_pool == v_pool && kVBuffers == 2;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
                  int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*,
                  const float*) =
-      early ? (cluster ? decode_attention_kernel<true, true> : decode_attention_kernel<false, true>)
-            : (cluster ? decode_attention_kernel<true, false> : decode_attention_kernel<false, false>);
+      alias ? (early ? (cluster ? decode_attention_kernel<true, true, true> : decode_attention_kernel<false, true, true>)
+                     : (cluster ? decode_attention_kernel<true, false, true> : decode_attention_kernel<false, false, true>))
+            : (early ? (cluster ? decode_attention_kernel<true, true, false> : decode_attention_kernel<false, true, false>)
+                     : (cluster ? decode_attention_kernel<true, false, false> : decode_attention_kernel<false, false, false>));
   if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
-    static bool configured[64][4] = {};
+    static bool configured[64][8] = {};
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
-    if (!configured[device][2 * early + cluster]) {
+    if (!configured[device][4 * alias + 2 * early + cluster]) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
       if (err != cudaSuccess) return (int)err;
-      configured[device][2 * early + cluster] = true;
+      configured[device][4 * alias + 2 * early + cluster] = true;
     }
   }
   dim3 grid((unsigned)most, nkv, n_rows);

@@ -61,16 +61,26 @@ min_gru_scan_kernel(const TI* __restrict__ proj, const float* __restrict__ bias,
   __syncthreads();
   for (int t0 = first; t0 < last; t0 += ty * K) {
     const int mine = t0 + y * K;
+    // all of the run's loads first (3 K independent loads a thread in flight), then the arithmetic,
+    // in place: a = 1 - z, b = z * candidate, gate = silu(g)
     float a[K], b[K], gate[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int t = mine + k;
+      const bool on = live && t < last;
+      const TI* row = proj + (size_t)(on ? t : first) * ld;
+      a[k] = on ? to_float(row[z_at + c]) : 0.f;
+      b[k] = on ? to_float(row[u_at + c]) : 0.f;
+      gate[k] = on ? to_float(row[g_at + c]) : 0.f;
+    }
     float p = 1.f, acc = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int t = mine + k;
       if (live && t < last) {
-        const TI* row = proj + (size_t)t * ld;
-        const float z = rec_sigmoid<FAST>(to_float(row[z_at + c]) + bz);
-        const float u = to_float(row[u_at + c]) + bu;
-        const float g = to_float(row[g_at + c]) + bg;
+        const float z = rec_sigmoid<FAST>(a[k] + bz);
+        const float u = b[k] + bu;
+        const float g = gate[k] + bg;
         const float cand = u >= 0.f ? u + 0.5f : rec_sigmoid<FAST>(u);
         a[k] = 1.0f - z;
         b[k] = z * cand;
