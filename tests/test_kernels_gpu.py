@@ -240,8 +240,8 @@ def test_attention_refuses_sizes_it_cannot_take():
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(ValueError, match="do not divide"):
         ops().paged_attention_generic(q, pool, pool, q.clone(), table, z, z, 6, 4, 16, 16, None, 1.0)
-    with pytest.raises(ValueError, match="beyond 512"):
-        ops().paged_attention_generic(q, pool, pool, q.clone(), table, z, z, 1, 1, 1024, 16, None, 1.0)
+    with pytest.raises(ValueError, match="beyond 1024"):
+        ops().paged_attention_generic(q, pool, pool, q.clone(), table, z, z, 1, 1, 2048, 16, None, 1.0)
 
 
 def test_argmax_ties_and_sampling_against_the_plain_rule():

@@ -212,6 +212,7 @@ def sink_reference(q, dense, row_req, pos, heads, window, scale, sink):
 
 @pytest.mark.parametrize("kernel,dtype,heads,row,window", [
     ("generic", torch.float32, 3, 48, None), ("generic", torch.bfloat16, 17, 144, 20), ("generic", torch.float32, 5, 32, 6),
+    ("generic", torch.bfloat16, 2, 640, None),
     ("decode", torch.bfloat16, 5, 32, None), ("decode", torch.bfloat16, 16, 64, 32), ("decode", torch.bfloat16, 2, 128, None),
     ("tiles", torch.bfloat16, 3, 48, 6), ("tiles", torch.bfloat16, 4, 80, None),
     ("wide", torch.bfloat16, 2, 128, None), ("wide", torch.bfloat16, 6, 128, 95), ("wide", torch.bfloat16, 3, 64, None)])

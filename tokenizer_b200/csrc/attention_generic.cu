@@ -18,7 +18,7 @@
 
 #define ATT_THREADS 128
 #define ATT_CHUNK 128
-#define ATT_MAX_HEAD_DIM 512
+#define ATT_MAX_HEAD_DIM 1024
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS)

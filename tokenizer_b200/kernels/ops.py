@@ -318,8 +318,8 @@ def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, n
     """`sink` (float32, one per query head): a score without key or value that counts once in
     the softmax's denominator, unscaled.  `v_pool` may be `k_pool` itself (values that are the
     leading lanes of the key rows)."""
-    if d > 512:
-        raise ValueError(f"attention: head size {d} is beyond 512")
+    if d > 1024:
+        raise ValueError(f"attention: head size {d} is beyond 1024")
     if nh % nkv:
         raise ValueError(f"attention: {nh} heads do not divide into {nkv} groups")
     _check(_lib("attention_generic").tokb200_paged_attention_generic(
