@@ -130,6 +130,27 @@ def test_gated_delta_takes_a_product_whole_or_in_partial_sums():
           torch.float32)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,partials", [(50, 0), (1030, 3), (4500, 2), (256, 0)])
+def test_gate_residual_add_and_norm_in_one_kernel(dtype, hidden, partials):
+    rows = 7
+    x = rnd(rows, hidden, seed=30)
+    before = x.clone()
+    wide = rnd(rows, 12 + hidden, seed=31, scale=2.0)
+    pre, pre_bias, gain = wide[:, 12:], rnd(hidden, seed=32), rnd(hidden, seed=33) + 1.0
+    if partials:
+        y, bias = rnd(partials, rows, hidden, seed=34), rnd(hidden, seed=35)
+        total = y.double().cpu().sum(0) + bias.double().cpu()
+    else:
+        y, bias = rnd(rows, hidden, seed=34, dtype=torch.bfloat16), None
+        total = y.double().cpu()
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    ops().gated_add_rms_norm(x, y, bias, pre, pre_bias, gain, 1e-5, out)
+    want_x = before.double().cpu() + total * torch.sigmoid(pre.double().cpu() + pre_bias.double().cpu())
+    close(x, want_x, torch.float32, "the stream after the add")
+    close(out, plain.rms_norm(want_x, gain.double().cpu(), 1e-5), dtype, "the normed rows")
+
+
 # ---- the kernels around the cached latent -------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("q_rank,kv_rank,rot_dim,rot_dims", [(40, 48, 0, 0), (56, 24, 8, 8), (20, 130, 10, 6)])

@@ -229,3 +229,166 @@ TOKB200_API int tokb200_gated_delta(const void* y, int y_dtype, int n_partials, 
 #undef LAUNCH
   return TOKB200_BAD_DTYPE;
 }
+
+// ---- the gate, the residual add and the norm that follows, in one pass over the row ----
+// x[t,:] += (sum_s y[s,t,:] + bias) * sigmoid(pre[t,:] + pre_bias);  out[t,:] = x / sqrt(mean(x^2) + eps) * gain.
+// A block a row; a thread keeps up to GN_KEEP of its lanes' new values in registers between the sum
+// of squares and the result (rows beyond 256 * GN_KEEP lanes read the rest back from x).
+#define GN_KEEP 16
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+gated_add_rms_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, int n_partials, size_t partial_stride,
+                          const float* __restrict__ bias, const float* __restrict__ pre,
+                          const float* __restrict__ pre_bias, int ld_pre, const float* __restrict__ gain,
+                          float eps, TO* __restrict__ out, int hidden) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  pdl_wait();
+  pdl_launch();
+  float* row = x + (size_t)t * hidden;
+  const float* gate = pre + (size_t)t * ld_pre;
+  float kept[GN_KEEP];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < GN_KEEP; ++k) {
+    const int c = threadIdx.x + k * 256;
+    kept[k] = 0.f;
+    if (c < hidden) {
+      float v = 0.f;
+      for (int s = 0; s < n_partials; ++s) v += to_float(y[(size_t)s * partial_stride + (size_t)t * hidden + c]);
+      if (bias) v += bias[c];
+      const float g = gate[c] + (pre_bias ? pre_bias[c] : 0.f);
+      const float now = row[c] + v / (1.0f + expf(-g));
+      row[c] = now;
+      kept[k] = now;
+      sq += now * now;
+    }
+  }
+  for (int c = threadIdx.x + GN_KEEP * 256; c < hidden; c += 256) {
+    float v = 0.f;
+    for (int s = 0; s < n_partials; ++s) v += to_float(y[(size_t)s * partial_stride + (size_t)t * hidden + c]);
+    if (bias) v += bias[c];
+    const float g = gate[c] + (pre_bias ? pre_bias[c] : 0.f);
+    const float now = row[c] + v / (1.0f + expf(-g));
+    row[c] = now;
+    sq += now * now;
+  }
+  sq = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(sq / (float)hidden + eps);
+  TO* dst = out + (size_t)t * hidden;
+#pragma unroll
+  for (int k = 0; k < GN_KEEP; ++k) {
+    const int c = threadIdx.x + k * 256;
+    if (c < hidden) dst[c] = from_float<TO>(kept[k] * inv * gain[c]);
+  }
+  for (int c = threadIdx.x + GN_KEEP * 256; c < hidden; c += 256) dst[c] = from_float<TO>(row[c] * inv * gain[c]);
+}
+
+// The same in 16-byte pieces: rows of a multiple of 4 lanes up to 256 * 4 * GN_QUADS, every pointer
+// 16-byte aligned.  All of a piece's loads (the planes of y, x, the gate) are independent and issued
+// together; the new values stay in registers for the result.
+#define GN_QUADS 8
+__device__ __forceinline__ float4 gn_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 gn_load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+gated_add_rms_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, int n_partials, size_t partial_stride,
+                              const float* __restrict__ bias, const float* __restrict__ pre,
+                              const float* __restrict__ pre_bias, int ld_pre, const float* __restrict__ gain,
+                              float eps, TO* __restrict__ out, int hidden) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int quads = hidden / 4;
+  pdl_wait();
+  pdl_launch();
+  float* row = x + (size_t)t * hidden;
+  const float* gate = pre + (size_t)t * ld_pre;
+  const TY* y_row = y + (size_t)t * hidden;
+  float4 kept[GN_QUADS];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < GN_QUADS; ++k) {
+    const int c = (threadIdx.x + k * 256) * 4;
+    kept[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < hidden) {
+      float4 v = gn_load4(y_row + c);
+#pragma unroll 8
+      for (int s = 1; s < n_partials; ++s) {
+        const float4 p = gn_load4(y_row + (size_t)s * partial_stride + c);
+        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+      }
+      float4 g = gn_load4(gate + c);
+      const float4 old = gn_load4(row + c);
+      if (bias) { const float4 b = gn_load4(bias + c); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+      if (pre_bias) { const float4 b = gn_load4(pre_bias + c); g.x += b.x; g.y += b.y; g.z += b.z; g.w += b.w; }
+      float4 now;
+      now.x = old.x + v.x / (1.0f + expf(-g.x));
+      now.y = old.y + v.y / (1.0f + expf(-g.y));
+      now.z = old.z + v.z / (1.0f + expf(-g.z));
+      now.w = old.w + v.w / (1.0f + expf(-g.w));
+      *reinterpret_cast<float4*>(row + c) = now;
+      kept[k] = now;
+      sq += now.x * now.x + now.y * now.y + now.z * now.z + now.w * now.w;
+    }
+  }
+  sq = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(sq / (float)hidden + eps);
+  TO* dst = out + (size_t)t * hidden;
+#pragma unroll
+  for (int k = 0; k < GN_QUADS; ++k) {
+    const int c = (threadIdx.x + k * 256) * 4;
+    if (c < hidden) {
+      const float4 w = gn_load4(gain + c);
+      const float r0 = kept[k].x * inv * w.x, r1 = kept[k].y * inv * w.y;
+      const float r2 = kept[k].z * inv * w.z, r3 = kept[k].w * inv * w.w;
+      if constexpr (sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(dst + c) = make_float4(r0, r1, r2, r3);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+        uint2 packed;
+        packed.x = *reinterpret_cast<unsigned*>(&lo);
+        packed.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(dst + c) = packed;
+      }
+    }
+  }
+  (void)quads;
+}
+
+TOKB200_API int tokb200_gated_add_rms_norm(float* x, const void* y, int y_dtype, int n_partials,
+                                           long long partial_stride, const float* bias, const void* pre,
+                                           int pre_dtype, const float* pre_bias, int ld_pre, const float* gain,
+                                           float eps, void* out, int out_dtype, int n_rows, int hidden,
+                                           cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (hidden <= 0 || ld_pre < hidden || n_partials < 1) return TOKB200_BAD_SIZE;
+  if (pre_dtype != TOKB200_F32) return TOKB200_BAD_DTYPE;
+  if (hidden % 4 == 0 && hidden <= 256 * 4 * GN_QUADS && ld_pre % 4 == 0 && partial_stride % 4 == 0 &&
+      (((uintptr_t)x | (uintptr_t)y | (uintptr_t)bias | (uintptr_t)pre | (uintptr_t)pre_bias | (uintptr_t)gain |
+        (uintptr_t)out) & 15) == 0) {
+#define LAUNCH_VEC(TY, TO)                                                                              \
+  return launch_dependent(gated_add_rms_norm_vec_kernel<TY, TO>, dim3(n_rows), dim3(256), 0, stream, x, \
+                          (const TY*)y, n_partials, (size_t)partial_stride, bias, (const float*)pre,    \
+                          pre_bias, ld_pre, gain, eps, (TO*)out, hidden)
+    if (y_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH_VEC(float, float);
+    if (y_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH_VEC(float, __nv_bfloat16);
+    if (y_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH_VEC(__nv_bfloat16, __nv_bfloat16);
+    if (y_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH_VEC(__nv_bfloat16, float);
+#undef LAUNCH_VEC
+  }
+#define LAUNCH(TY, TO)                                                                                  \
+  return launch_dependent(gated_add_rms_norm_kernel<TY, TO>, dim3(n_rows), dim3(256), 0, stream, x,     \
+                          (const TY*)y, n_partials, (size_t)partial_stride, bias, (const float*)pre,    \
+                          pre_bias, ld_pre, gain, eps, (TO*)out, hidden)
+  if (y_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
+  if (y_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  if (y_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (y_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return TOKB200_BAD_DTYPE;
+}

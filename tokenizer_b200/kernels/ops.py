@@ -1053,6 +1053,22 @@ def gated_delta(y: torch.Tensor, bias: Optional[torch.Tensor], pre: torch.Tensor
         _sliced_ptr(pre_bias) if pre_bias is not None else _ptr(None), _i(_ld(pre)), _ptr(out), _i(n_rows), _i(hidden), _stream()), "gated_delta")
 
 
+def gated_add_rms_norm(x: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor], pre: torch.Tensor,
+                       pre_bias: Optional[torch.Tensor], gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """x += (y + bias) * sigmoid(pre + pre_bias) in place (x float32 [T, H]; y, bias, pre, pre_bias as
+    for `gated_delta`), then out = x / sqrt(mean(x^2) + eps) * gain: the gate, the residual add and the
+    norm that follows in one pass over the row."""
+    n_rows, hidden = x.shape
+    if x.dtype != torch.float32 or gain.dtype != torch.float32 or gain.numel() != hidden or \
+            tuple(out.shape) != (n_rows, hidden) or tuple(pre.shape) != (n_rows, hidden):
+        raise ValueError("gated_add_rms_norm: x float32 [T, H], a float32 gain of H, out and the gate [T, H]")
+    n_partials, stride = _partials(y, x)
+    _check(_lib("activation").tokb200_gated_add_rms_norm(
+        _ptr(x), _ptr(y), _i(_tag(y)), _i(n_partials), _ll(stride), _ptr(bias), _sliced_ptr(pre), _i(_tag(pre)),
+        _sliced_ptr(pre_bias) if pre_bias is not None else _ptr(None), _i(_ld(pre)), _ptr(gain), _f(eps),
+        _ptr(out), _i(_tag(out)), _i(n_rows), _i(hidden), _stream()), "gated_add_rms_norm")
+
+
 def latent_prepare(proj: torch.Tensor, q_at: int, q_rank: int, c_at: int, kv_rank: int, rot_dim: int,
                    rot_dims: int, q_gain, c_gain, eps: float, inv_freq, pos, row_req, slot, q_latent, pool) -> None:
     """From one projection's rows: the normed query latent (dense, `q_latent` [T, q_rank]) and the

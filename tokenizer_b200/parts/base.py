@@ -206,28 +206,70 @@ class CacheBinding:
 
 
 # --------------------------------------------------------------------------- #
+@dataclass
+class GatedDelta:
+    """A sublayer's output that is still to be scaled by its gate: (y + bias) * sigmoid(pre +
+    pre_bias), with y [T, H] or float32 partial sums [S, T, H], pre float32 [T, H] (possibly a
+    column slice of a wider product) and the biases float32 [H] or None."""
+
+    y: torch.Tensor
+    bias: Optional[torch.Tensor]
+    pre: torch.Tensor
+    pre_bias: Optional[torch.Tensor]
+
+
 class ResidualStream:
     """The residual sum, kept in float32.  A part's output is not added at once:
     it stays pending until the next norm, which adds it while it reads the row
-    (one pass over memory instead of two)."""
+    (one pass over memory instead of two).  A gated output (`add_gated`) stays pending with its
+    gate unapplied: a norm that offers `forward_gated` applies the gate, adds and norms in one
+    kernel; anything else that asks for `pending` gets the gated product as a float32 tensor."""
 
     def __init__(self, x: torch.Tensor):
         if x.dtype != torch.float32:
             raise ValueError("the residual stream is float32")
         self.x = x
-        self.pending: Optional[torch.Tensor] = None
+        self._pending: Optional[torch.Tensor] = None
+        self._gated: Optional[GatedDelta] = None
+
+    @property
+    def pending(self) -> Optional[torch.Tensor]:
+        if self._gated is not None:
+            g, self._gated = self._gated, None
+            self._pending = torch.empty(self.x.shape, dtype=torch.float32, device=self.x.device)
+            ops.gated_delta(g.y, g.bias, g.pre, self._pending, pre_bias=g.pre_bias)
+        return self._pending
+
+    @pending.setter
+    def pending(self, value: Optional[torch.Tensor]) -> None:
+        self._pending, self._gated = value, None
 
     def add(self, delta: torch.Tensor) -> None:
         self.flush()
         self.pending = delta
 
+    def add_gated(self, delta: GatedDelta) -> None:
+        self.flush()
+        self._gated = delta
+
     def flush(self) -> torch.Tensor:
-        if self.pending is not None:
-            ops.residual_add(self.x, self.pending)
+        pending = self.pending
+        if pending is not None:
+            ops.residual_add(self.x, pending)
             self.pending = None
         return self.x
 
+    # Up to this many rows the gate, the add and the norm run as one kernel (a decoding step is
+    # bound by its launches: 0.290 -> 0.274 ms a step of 8 rows at width 1,024); with more rows the
+    # gate's own kernel and the norm that adds a pending tensor are faster together (a step of 2,048
+    # tokens at width 2,048: 2.29 against 2.36 ms), both moving 16 bytes a thread over many blocks.
+    GATED_NORM_ROWS = 64
+
     def normed(self, norm) -> torch.Tensor:
+        fused = getattr(norm, "forward_gated", None)
+        if self._gated is not None and fused is not None and self.x.shape[0] <= self.GATED_NORM_ROWS:
+            gated, self._gated = self._gated, None
+            return fused(self.x, gated)
         delta, self.pending = self.pending, None
         return norm.forward(self.x, delta=delta)
 

@@ -7,7 +7,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.store import TensorSpec
-from .base import register_part
+from .base import GatedDelta, register_part
 from .linear import Linear
 
 
@@ -85,7 +85,8 @@ class ResidualGate:
 class GatedPreNormResidual:
     """x += mixer(norm1(x)) * gate1(norm1(x)); x += feed_forward(norm2(x)) * gate2(norm2(x)).  The
     gates' products ride in the sublayers' first products where those offer it; the gated outputs
-    are float32 and stay pending on the stream, so that the next norm adds them."""
+    stay pending on the stream with their gates unapplied, so that the next norm applies the gate,
+    adds and norms in one kernel."""
 
     PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_gate": "gate",
              "feed_forward": "feed_forward", "feed_forward_norm": "norm", "feed_forward_gate": "gate"}
@@ -111,10 +112,8 @@ class GatedPreNormResidual:
     def _gated(self, stream, part, gate, h, y):
         carried = id(part) in self._carried
         pre = part.side_pre if carried else gate.forward(h)
-        delta = torch.empty(stream.x.shape, dtype=torch.float32, device=stream.x.device)
-        ops.gated_delta(y, getattr(part, "deferred_bias", None), pre, delta,
-                        pre_bias=part.side_bias if carried else None)
-        stream.add(delta)
+        stream.add_gated(GatedDelta(y, getattr(part, "deferred_bias", None), pre,
+                                    part.side_bias if carried else None))
 
     def forward(self, stream, ctx, cache):
         h = stream.normed(self.mixer_norm)

@@ -35,6 +35,12 @@ class RMSNorm:
         """(gain, eps) for a consumer that computes this norm inside its own kernel."""
         return self.gain, self.eps
 
+    def forward_gated(self, x, gated):
+        """x += (y + bias) * sigmoid(pre + pre_bias), then the norm of the new x: one kernel."""
+        out = self.runtime.empty(x.shape[0], self.size)
+        ops.gated_add_rms_norm(x, gated.y, gated.bias, gated.pre, gated.pre_bias, self.gain, self.eps, out)
+        return out
+
     def forward(self, x, delta=None, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.empty(n, self.size)
