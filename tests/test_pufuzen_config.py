@@ -45,7 +45,8 @@ def test_the_architecture_is_chosen_by_its_name_and_every_size_comes_from_the_fi
     (lambda r: r["layers"][1]["mixer"].pop("kv_rank"), "kv_rank"),
     (lambda r: r["layers"][2]["mixer"]["rot"].update(dims=6), "rot.dims"),
     (lambda r: r["layers"][2]["mixer"]["rot"].update(dims=3), "rot.dims"),
-    (lambda r: r.pop("logit_scale"), "logit_scale"),
+    (lambda r: r.update(logit_scale="two"), "logit_scale"),
+    (lambda r: r.pop("norm"), "norm"),
     (lambda r: r["layers"][1]["mixer"]["mask"].update(size=0), "size"),
     (lambda r: r["layers"][1]["mixer"].update(mask=7), "mask"),
 ])

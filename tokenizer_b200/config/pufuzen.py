@@ -39,7 +39,7 @@ class PufuzenConfig:
         self.raw = raw
         self.vocab = as_int(raw, "vocab", 1)
         self.width = as_int(raw, "width", 1)
-        self.logit_scale = as_float(raw, "logit_scale")
+        self.logit_scale = as_float(raw, "logit_scale") if raw.get("logit_scale") is not None else 1.0
         if not isinstance(raw["norm"], dict) or "eps" not in raw["norm"]:
             raise ConfigError("config.json norm must be an object with eps")
         self.eps = as_float(raw["norm"], "eps")
@@ -88,7 +88,7 @@ class PufuzenConfig:
 
     @classmethod
     def from_dict(cls, raw: Dict[str, Any]) -> "PufuzenConfig":
-        require_keys(raw, ["vocab", "width", "layers", "logit_scale", "norm"], ARCHITECTURE)
+        require_keys(raw, ["vocab", "width", "layers", "norm"], ARCHITECTURE)      # no logit_scale: 1
         return cls(copy.deepcopy(raw))
 
     def to_dict(self) -> Dict[str, Any]:
