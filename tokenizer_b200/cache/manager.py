@@ -2,11 +2,12 @@
 and slots for per-request state of fixed size.
 
 Calls of the model's order whose mixers need the same kind of storage (the
-same kv heads, head size and window) form a *group*.  A group owns its pages
+same kv heads, head size, window and chunk size) form a *group*.  A group owns its pages
 (an allocator and one device pool) and every request has one block table per
 group, because groups differ in what they keep: a group of all keys keeps every
 page of a request, a group with a window gives a page back as soon as the
-window has passed it.  Inside a group every call has its own layer of the pool,
+window has passed it, a group whose keys are read inside chunks as soon as a request's next
+position lies in a later chunk.  Inside a group every call has its own layer of the pool,
 addressed by the same table.  Beside the pages the manager owns the state
 arenas: one tensor [state slots, *shape] per call whose mixer declares state;
 a request takes one slot index when it opens (zeroed) and returns it when it
@@ -30,7 +31,13 @@ class GroupLayout:
     head_dim: int
     window: Optional[int]
     planes: int = 2                                  # rows a token stores per call (keys and values, or one for both)
+    chunk: Optional[int] = None                      # keys are read inside chunks of this many positions only
     calls: List[int] = field(default_factory=list)   # calls of the order that write here
+
+    @property
+    def keeps_all(self) -> bool:
+        """No page of a request is given back before the request ends."""
+        return self.window is None and self.chunk is None
 
 
 @dataclass
@@ -59,12 +66,12 @@ def plan_groups(needs) -> (List[GroupLayout], List[Optional[int]]):
         if need is None or need.kv is None:
             group_of.append(None)
             continue
-        key = (need.kv.kv_heads, need.kv.head_dim, need.kv.window, need.kv.planes)
+        key = (need.kv.kv_heads, need.kv.head_dim, need.kv.window, need.kv.planes, need.kv.chunk)
         for g, layout in enumerate(groups):
-            if (layout.kv_heads, layout.head_dim, layout.window, layout.planes) == key:
+            if (layout.kv_heads, layout.head_dim, layout.window, layout.planes, layout.chunk) == key:
                 break
         else:
-            groups.append(GroupLayout(*key))
+            groups.append(GroupLayout(need.kv.kv_heads, need.kv.head_dim, need.kv.window, need.kv.planes, need.kv.chunk))
             g = len(groups) - 1
         groups[g].calls.append(call)
         group_of.append(g)
@@ -85,7 +92,7 @@ class CachePlan:
         self.allocators = [PageAllocator(num_pages, page_size) for _ in self.groups]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: Dict[object, RequestCache] = {}
-        shareable = len(self.groups) == 1 and self.groups[0].window is None and not self.state_calls
+        shareable = len(self.groups) == 1 and self.groups[0].keeps_all and not self.state_calls
         self.share_prefixes = bool(share_prefixes and shareable)
 
     # ---- requests ------------------------------------------------------------
@@ -104,10 +111,11 @@ class CachePlan:
 
     def first_needed_block(self, group: int, position: int) -> int:
         """The first logical block a query at `position` can still read."""
-        window = self.groups[group].window
-        if window is None:
-            return 0
-        return max(0, position - window) // self.page_size
+        window, chunk = self.groups[group].window, self.groups[group].chunk
+        first = 0 if window is None else max(0, position - window)
+        if chunk is not None:
+            first = max(first, position - position % chunk)      # the start of the position's own chunk
+        return first // self.page_size
 
     def pages_missing(self, cache: RequestCache, n_new: int) -> List[int]:
         """Per group, the pages a step of `n_new` more tokens still needs."""
@@ -115,7 +123,7 @@ class CachePlan:
         end_block = pages_for(cache.length + n_new, self.page_size)
         for g in range(len(self.groups)):
             table = cache.tables[g]
-            if self.groups[g].window is None:
+            if self.groups[g].keeps_all:
                 # a table of all keys has no holes (every reserve fills it from block 0 on and
                 # nothing is given back before the end): only blocks past its end are missing
                 missing.append(max(0, end_block - len(table)))
@@ -143,7 +151,7 @@ class CachePlan:
         end_block = pages_for(cache.length + n_new, self.page_size)
         for g, allocator in enumerate(self.allocators):
             table = cache.tables[g]
-            if self.groups[g].window is None:
+            if self.groups[g].keeps_all:
                 while len(table) < end_block:          # no holes below the table's end (see pages_missing)
                     table.append(allocator.take())
                 continue
@@ -159,7 +167,7 @@ class CachePlan:
         every later query's window has passed are given back."""
         cache.length += n_new
         for g, allocator in enumerate(self.allocators):
-            if self.groups[g].window is None:
+            if self.groups[g].keeps_all:
                 continue
             table = cache.tables[g]
             for b in range(min(self.first_needed_block(g, cache.length), len(table))):
@@ -226,7 +234,7 @@ class CachePlan:
                 for page in cache.tables[g]:
                     if page >= 0:
                         counts[page] = counts.get(page, 0) + 1
-                    elif self.groups[g].window is None:
+                    elif self.groups[g].keeps_all:
                         raise PageError(f"group {g} keeps all keys, yet request "
                                         f"{cache.request_id!r} has a hole in its table")
             for page in range(allocator.capacity):

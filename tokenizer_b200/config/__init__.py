@@ -3,9 +3,10 @@ from .registry import (config_class_for, config_from_dict, load_config, register
                        registered_architectures)
 from .qwen2 import Qwen2Config
 from .pufuzen import PufuzenConfig
+from .katopel import KatopelConfig
 
 __all__ = [
-    "ConfigError", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "PufuzenConfig", "Qwen2Config",
+    "ConfigError", "KatopelConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "PufuzenConfig", "Qwen2Config",
     "config_class_for", "config_from_dict", "load_config", "register_architecture",
     "registered_architectures",
 ]

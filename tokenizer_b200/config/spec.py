@@ -69,10 +69,14 @@ class LayerCall:
     """One entry of the run order.  `layer` indexes `ModelSpec.layers`.
     `cache` names the cache slot the mixer uses at this call: by default a slot
     of its own (the index of the call in the order); the index of an earlier
-    call makes the mixer read that call's cache instead of writing one."""
+    call makes the mixer read that call's cache instead of writing one.  A layer may be called
+    several times (a looped stack): every call then has a cache and state of its own."""
 
     layer: int
     cache: Optional[int] = None
+    # a part of category "injection" that touches the residual stream right before this call's
+    # layer (what a pass of a looped stack adds before its first layer), or None
+    before: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -113,7 +113,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ row_req, const int* __restrict__ pos, int nh,
-                        int nkv, int page, int window, float scale,
+                        int nkv, int page, int window, int key_chunk, float scale,
                         float* __restrict__ scratch, int* __restrict__ counters, int min_chunk,
                         const int* __restrict__ rows, const float* __restrict__ sink) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
@@ -127,7 +127,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int row = rows ? rows[z] : z;
   const int r = row < 0 ? -1 : row_req[row];
   const int p = r < 0 ? 0 : pos[row];
-  const int lo = (window >= 0 && p - window > 0) ? p - window : 0;
+  const int lo = first_visible_key(p, window, key_chunk);
   const int n_keys = p - lo + 1;
   const int chunk = split_chunk(n_keys, min_chunk);
   const int n_splits = (n_keys + chunk - 1) / chunk;
@@ -497,7 +497,7 @@ TOKB200_API int tokb200_decode_attention_head_dim() { return HEAD_DIM; }
 TOKB200_API int tokb200_decode_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, int n_rows, int nh, int nkv, int d,
-    int page, int window, float scale, float* scratch, int* counters, const int* rows,
+    int page, int window, int key_chunk, float scale, float* scratch, int* counters, const int* rows,
     const float* sink, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > DEC_MAX_GROUP || page <= 0 ||
@@ -513,6 +513,7 @@ TOKB200_API int tokb200_decode_attention(
   // more pieces than this; blocks beyond would only find that out and leave
   long long reach = (long long)table_stride * page;
   if (window >= 0 && window + 1 < reach) reach = window + 1;
+  if (key_chunk > 0 && key_chunk < reach) reach = key_chunk;
   // The shortest piece for this launch: the candidate (a whole number of passes of 256 keys)
   // with the least estimated time, from a block's fixed cost (3), 2 per pass of 256 keys at head
   // size 64 (in proportion for others), 3 for a merge across blocks, and as many waves as the
@@ -570,7 +571,7 @@ TOKB200_API int tokb200_decode_attention(
   // one pool read as keys and as values, while a warp has two staging buffers (see ALIAS)
   const bool alias = k_pool == v_pool && kVBuffers == 2;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
-                 int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*,
+                 int, const int*, const int*, int, int, int, int, int, float, float*, int*, int, const int*,
                  const float*) =
       alias ? (early ? (cluster ? decode_attention_kernel<true, true, true> : decode_attention_kernel<false, true, true>)
                      : (cluster ? decode_attention_kernel<true, false, true> : decode_attention_kernel<false, false, true>))
@@ -591,7 +592,7 @@ TOKB200_API int tokb200_decode_attention(
     return launch_dependent(kernel, grid, dim3(DEC_THREADS), smem, stream,
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
-                            table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
+                            table_stride, row_req, pos, nh, nkv, page, window, key_chunk, scale, scratch,
                             counters, min_chunk, rows, sink);
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
@@ -613,7 +614,7 @@ TOKB200_API int tokb200_decode_attention(
   config.numAttrs = 2;
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                        (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
-                                       table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
+                                       table_stride, row_req, pos, nh, nkv, page, window, key_chunk, scale, scratch,
                                        counters, min_chunk, rows, sink);
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }

@@ -26,7 +26,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const T* __restrict__ v_pool, T* __restrict__ out,
                                const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ row_req, const int* __restrict__ pos,
-                               int nh, int nkv, int d, int page, int window, float scale,
+                               int nh, int nkv, int d, int page, int window, int chunk, float scale,
                                const float* __restrict__ sink) {
   extern __shared__ float smem[];
   float* q_s = smem;                 // d
@@ -39,7 +39,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   if (r < 0) return;
   const int p = pos[t];
   const int kvh = h / (nh / nkv);
-  const int lo = (window >= 0 && p - window > 0) ? p - window : 0;
+  const int lo = first_visible_key(p, window, chunk);
   const int* table = block_table + (size_t)r * table_stride;
 
   const T* q_row = q + ((size_t)t * nh + h) * d;
@@ -96,7 +96,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 TOKB200_API int tokb200_paged_attention_generic(
     const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
     const int* block_table, int table_stride, const int* row_req, const int* pos, int n_rows,
-    int nh, int nkv, int d, int page, int window, float scale, const float* sink,
+    int nh, int nkv, int d, int page, int window, int chunk, float scale, const float* sink,
     cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d <= 0 || d > ATT_MAX_HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 ||
@@ -107,12 +107,12 @@ TOKB200_API int tokb200_paged_attention_generic(
   if (dtype == TOKB200_F32)
     paged_attention_generic_kernel<float><<<grid, ATT_THREADS, smem, stream>>>(
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table,
-        table_stride, row_req, pos, nh, nkv, d, page, window, scale, sink);
+        table_stride, row_req, pos, nh, nkv, d, page, window, chunk, scale, sink);
   else if (dtype == TOKB200_BF16)
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, nh, nkv, d, page, window,
-        scale, sink);
+        chunk, scale, sink);
   else
     return TOKB200_BAD_DTYPE;
   return tokb200_launch_status();

@@ -106,7 +106,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page,
-                         int window, float scale_log2, const float* __restrict__ sink) {
+                         int window, int chunk, float scale_log2, const float* __restrict__ sink) {
   extern __shared__ __align__(16) __nv_bfloat16 smem[];
   __nv_bfloat16* q_s = smem;                       // [64][kStride]
   __nv_bfloat16* k_s = q_s + kTile;                // PF_STAGES tiles
@@ -123,7 +123,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int kvh = h / (nh / nkv);
   const int pos0 = pos[row0];
   const int pos_last = pos0 + n_rows - 1;
-  const int lo_first = (window >= 0 && pos0 - window > 0) ? pos0 - window : 0;  // first key any row sees
+  const int lo_first = first_visible_key(pos0, window, chunk);  // first key any row sees
+  const int lo_last = first_visible_key(pos_last, window, chunk);  // first key the last row sees
   const int* table = block_table + (size_t)r * table_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -157,7 +158,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     p_row[i] = pos0 + min(my_row[i], n_rows - 1);       // rows past the tile repeat its last row
-    lo_row[i] = (window >= 0 && p_row[i] - window > 0) ? p_row[i] - window : 0;
+    lo_row[i] = first_visible_key(p_row[i], window, chunk);
   }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[HEAD_DIM / 8][4];
@@ -214,7 +215,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
     // ---- mask (only in blocks that reach past a row's position or before its window),
     // running softmax on the raw scores: exp2(s * c - max * c), c = scale * log2(e) ----
-    const bool needs_mask = kb + PF_KEYS - 1 > pos0 || (window >= 0 && kb < pos_last - window);
+    const bool needs_mask = kb + PF_KEYS - 1 > pos0 || kb < lo_last;
     if (needs_mask) {
 #pragma unroll
       for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
@@ -317,7 +318,7 @@ TOKB200_API int tokb200_prefill_attention_head_dim() { return HEAD_DIM; }
 TOKB200_API int tokb200_prefill_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
-    int nkv, int d, int page, int window, float scale, const float* sink, cudaStream_t stream) {
+    int nkv, int d, int page, int window, int chunk, float scale, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || nh > 65535)
     return TOKB200_BAD_SIZE;
@@ -338,6 +339,6 @@ TOKB200_API int tokb200_prefill_attention(
   prefill_attention_kernel<<<grid, PF_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
       (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, tiles, n_tiles, nh, nkv, page,
-      window, scale_log2, sink);
+      window, chunk, scale_log2, sink);
   return tokb200_launch_status();
 }

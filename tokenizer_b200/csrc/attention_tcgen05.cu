@@ -201,7 +201,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page, int window,
-                         float scale_log2, const float* __restrict__ sink) {
+                         int chunk, float scale_log2, const float* __restrict__ sink) {
   extern __shared__ __align__(1024) unsigned char fa_raw[];      // swizzle atoms: 1024-byte aligned
   unsigned char* q_s = fa_raw;
   unsigned char* k_s = q_s + kQBytes;                            // FA_KV_BUFFERS buffers
@@ -233,7 +233,8 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int kvh = h / (nh / nkv);
   const int pos0 = live ? pos[row0] : 0;
   const int pos_last = pos0 + n_rows - 1;
-  const int lo_first = (window >= 0 && pos0 - window > 0) ? pos0 - window : 0;
+  const int lo_first = first_visible_key(pos0, window, chunk);
+  const int lo_last = first_visible_key(pos_last, window, chunk);
   const int kb_first = lo_first / FA_KEYS * FA_KEYS;
   const int n_blocks = live ? (pos_last - kb_first) / FA_KEYS + 1 : 0;
   const int* table = block_table + (size_t)(live ? r_id : 0) * table_stride;
@@ -367,7 +368,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int split = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
     const int p_row = pos0 + min(r, n_rows - 1);            // rows past the tile repeat its last row
-    const int lo_row = (window >= 0 && p_row - window > 0) ? p_row - window : 0;
+    const int lo_row = first_visible_key(p_row, window, chunk);
     const unsigned lane_base = ((unsigned)((warp & 3) * 32) << 16);
     const unsigned my_o = tmem_o + lane_base + (unsigned)(split * HEAD_DIM);
     float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (raw score units) and running sum
@@ -382,7 +383,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       for (int c0 = 0; c0 < kSplitKeys; c0 += 32)
         fa_tmem_load32(tmem_base + lane_base + (unsigned)((b & 1) * 128 + split * kSplitKeys + c0),
                        *reinterpret_cast<float(*)[32]>(&s[c0]));
-      const bool needs_mask = kb + kSplitKeys - 1 > pos0 || (window >= 0 && kb < pos_last - window);
+      const bool needs_mask = kb + kSplitKeys - 1 > pos0 || kb < lo_last;
       float m_blk = -INFINITY;
       if (needs_mask) {
 #pragma unroll
@@ -528,7 +529,7 @@ TOKB200_API int tokb200_attention_tcgen05_error(void) {
 TOKB200_API int tokb200_attention_tcgen05(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
-    int nkv, int d, int page, int window, float scale, const float* sink, cudaStream_t stream) {
+    int nkv, int d, int page, int window, int chunk, float scale, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0)
     return TOKB200_BAD_SIZE;
@@ -554,6 +555,6 @@ TOKB200_API int tokb200_attention_tcgen05(
   return launch_ordered(false, attention_tcgen05_kernel, grid, dim3(FA_THREADS), (size_t)kFaSmem, stream,
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table, table_stride,
-                          row_req, pos, tiles, n_tiles, nh, nkv, page, window,
+                          row_req, pos, tiles, n_tiles, nh, nkv, page, window, chunk,
                           scale * 1.4426950408889634f, sink);
 }

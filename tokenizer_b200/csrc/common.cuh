@@ -161,6 +161,18 @@ __device__ __forceinline__ float gate_activation(int kind, float g) {
   return fmaxf(g, 0.f);
 }
 
+// The first key a query at position p sees: 0; p - window where the layer has a window (window >= 0:
+// a key is hidden when key + window < query); the start of p's own chunk where keys are seen inside
+// chunks of `chunk` positions counted from 0 (chunk > 0); the later of the two where it has both.
+__device__ __forceinline__ int first_visible_key(int p, int window, int chunk) {
+  int lo = (window >= 0 && p - window > 0) ? p - window : 0;
+  if (chunk > 0) {
+    const int start = p - p % chunk;
+    lo = lo > start ? lo : start;
+  }
+  return lo;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

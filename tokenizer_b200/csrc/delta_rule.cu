@@ -1,0 +1,337 @@
+// The gated delta rule: a linear recurrence over a matrix state per head,
+//     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q        (S: dim x vdim, float32)
+// with q and k unit vectors per head (q also times dim^(-1/2)), beta in (0, 1) and a decay g in
+// (0, 1) per head and token, all of it 32-bit.  In front of it q, k and v pass a short causal
+// convolution over time, channel by channel, and silu; behind it every head's o is divided by its
+// root mean square, scaled by a gain and by silu of a gate projection.
+//
+// Per request the state slot holds, in float32: the heads' matrices TRANSPOSED and padded,
+// [heads, vdim, dim_padded] (a thread owns consecutive rows of one column, so that its share is
+// contiguous and a warp's loads coalesce), and behind them the convolution's last taps - 1 inputs,
+// [taps - 1, channels], oldest first.  A request's rows of a step are consecutive
+// (q_start[r] .. q_start[r + 1]); its state is read before its first row and written after its last.
+//
+//   gdn_prepare      a block a token: convolution (from the step's rows and, for a request's first
+//                    rows, from the kept inputs), silu, unit vectors, beta and the decay
+//   gdn_conv_state   the kept inputs move on (a thread a request and channel, after gdn_prepare)
+//   gdn_scan         the recurrence: the columns of S are independent, so thread (column j, part p)
+//                    keeps DPL rows of column j in registers; the P parts of a column add their
+//                    shares of S^T k and S^T q by shuffles.  Tokens are staged through shared memory
+//                    in runs, the next run's copies (cp.async) in flight behind the current one
+//   gdn_out_norm     a warp a (token, head): o / rms(o) * gain * scale * silu(gate)
+#include "common.cuh"
+
+#define GDN_MAX_TAPS 16
+#define GDN_THREADS 256
+
+__device__ __forceinline__ float gdn_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float gdn_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// proj: the stacked input product [T, ld]; columns qkv_at .. + channels are q (groups * dim), k
+// (groups * dim), v (heads * vdim); b_at .. + heads and a_at .. + heads the projections behind
+// beta and the decay.
+template <typename TI>
+__global__ void __launch_bounds__(GDN_THREADS)
+gdn_prepare_kernel(const TI* __restrict__ proj, int ld, int qkv_at, int b_at, int a_at, int groups, int heads,
+                   int dim, int vdim, int taps, const float* __restrict__ conv_w, const float* __restrict__ a_log,
+                   const float* __restrict__ dt_bias, const float* __restrict__ state, long long state_stride,
+                   int conv_off, const int* __restrict__ row_req, const int* __restrict__ q_start,
+                   const int* __restrict__ state_slot, float q_scale, float* __restrict__ qkv_out,
+                   float* __restrict__ bg_out) {
+  extern __shared__ float gdn_vals[];      // channels
+  const int t = blockIdx.x;
+  const int channels = 2 * groups * dim + heads * vdim;
+  const int r = row_req[t];
+  pdl_wait();
+  pdl_launch();
+  if (r < 0) return;
+  const int at = t - q_start[r];                      // the row's place in its request's portion
+  const float* kept = state + (size_t)state_slot[r] * state_stride + conv_off;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;                  // tap j weighs the input `back` tokens ago
+      const float in = back <= at ? to_float(proj[(size_t)(t - back) * ld + qkv_at + c])
+                                  : kept[(size_t)(taps - 1 - (back - at)) * channels + c];
+      acc += conv_w[(size_t)c * taps + j] * in;
+    }
+    gdn_vals[c] = acc * gdn_sigmoid(acc);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  float* out = qkv_out + (size_t)t * channels;
+  for (int h = warp; h < 2 * groups; h += warps) {   // q heads, then k heads
+    float ss = 0.f;
+    for (int l = lane; l < dim; l += 32) ss += gdn_vals[h * dim + l] * gdn_vals[h * dim + l];
+    ss = warp_sum(ss);
+    const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (h < groups ? q_scale : 1.0f);
+    for (int l = lane; l < dim; l += 32) out[h * dim + l] = gdn_vals[h * dim + l] * inv;
+  }
+  for (int c = 2 * groups * dim + threadIdx.x; c < channels; c += blockDim.x) out[c] = gdn_vals[c];
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    const float b = to_float(proj[(size_t)t * ld + b_at + h]);
+    const float a = to_float(proj[(size_t)t * ld + a_at + h]) + dt_bias[h];
+    bg_out[(size_t)t * 2 * heads + h] = gdn_sigmoid(b);
+    bg_out[(size_t)t * 2 * heads + heads + h] = expf(-expf(a_log[h]) * gdn_softplus(a));
+  }
+}
+
+template <typename TI>
+__global__ void gdn_conv_state_kernel(const TI* __restrict__ proj, int ld, int qkv_at, int channels, int taps,
+                                      float* __restrict__ state, long long state_stride, int conv_off,
+                                      const int* __restrict__ q_start, const int* __restrict__ state_slot) {
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int first = q_start[r], n = q_start[r + 1] - first;
+  pdl_wait();
+  pdl_launch();
+  if (n <= 0 || c >= channels) return;
+  float* kept = state + (size_t)state_slot[r] * state_stride + conv_off;
+  float old[GDN_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < GDN_MAX_TAPS; ++j) old[j] = j < taps - 1 ? kept[(size_t)j * channels + c] : 0.f;
+  // the last taps - 1 of (kept inputs, then the step's n inputs)
+#pragma unroll
+  for (int j = 0; j < GDN_MAX_TAPS; ++j) {
+    if (j < taps - 1) {
+      const int at = n + j;
+      float v = 0.f;
+      if (at >= taps - 1) {
+        v = to_float(proj[(size_t)(first + at - (taps - 1)) * ld + qkv_at + c]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < GDN_MAX_TAPS; ++i) v = i == at ? old[i] : v;
+      }
+      kept[(size_t)j * channels + c] = v;
+    }
+  }
+}
+
+__device__ __forceinline__ void gdn_copy4(float* dst, const float* src) {
+  const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(to), "l"(src) : "memory");
+}
+
+// qkv: [T, channels] as gdn_prepare wrote it; bg: [T, 2 heads] (beta, then the decay).
+// Block: `cols` columns of one head of one request, P parts a column (cols * P threads).
+template <int DPL>
+__global__ void __launch_bounds__(GDN_THREADS)
+gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int channels, int groups, int heads,
+                int dim, int vdim, int P, int cols, int run, float* __restrict__ state, long long state_stride,
+                const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ o_out) {
+  extern __shared__ __align__(16) float gdn_stage[];
+  const int dim_p = P * DPL;
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int col0 = blockIdx.x * cols;
+  const int part = threadIdx.x % P, col = threadIdx.x / P;
+  const int j = col0 + col;
+  const bool live = j < vdim;
+  const int first = q_start[r], last = q_start[r + 1];
+  pdl_wait();
+  pdl_launch();
+  if (first >= last) return;
+  // a buffer: k [run][dim_p], q [run][dim_p], v [run][cols], beta [run], decay [run]
+  const int per = run * (2 * dim_p + cols + 2);
+  for (int i = threadIdx.x; i < 2 * per; i += blockDim.x) gdn_stage[i] = 0.f;   // the padded lanes stay zero
+  __syncthreads();
+  const int g = h / (heads / groups);
+  const int k_col = (groups + g) * dim, q_col = g * dim, v_col = 2 * groups * dim + h * vdim + col0;
+  const int n_cols = min(cols, vdim - col0);
+  auto issue = [&](int c, int buf) {
+    float* k_s = gdn_stage + (size_t)buf * per;
+    float* q_s = k_s + run * dim_p;
+    float* v_s = q_s + run * dim_p;
+    float* b_s = v_s + run * cols;
+    float* g_s = b_s + run;
+    const int t0 = first + c * run;
+    const int n = min(run, last - t0);
+    for (int i = threadIdx.x; i < n * dim; i += blockDim.x) {
+      const int tok = i / dim, l = i % dim;
+      const float* row = qkv + (size_t)(t0 + tok) * channels;
+      gdn_copy4(&k_s[tok * dim_p + l], row + k_col + l);
+      gdn_copy4(&q_s[tok * dim_p + l], row + q_col + l);
+    }
+    for (int i = threadIdx.x; i < n * n_cols; i += blockDim.x) {
+      const int tok = i / n_cols, l = i % n_cols;
+      gdn_copy4(&v_s[tok * cols + l], qkv + (size_t)(t0 + tok) * channels + v_col + l);
+    }
+    for (int tok = threadIdx.x; tok < n; tok += blockDim.x) {
+      gdn_copy4(&b_s[tok], bg + (size_t)(t0 + tok) * 2 * heads + h);
+      gdn_copy4(&g_s[tok], bg + (size_t)(t0 + tok) * 2 * heads + heads + h);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float S[DPL];
+  float* mine = state + (size_t)state_slot[r] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim_p + part * DPL;
+#pragma unroll
+  for (int e = 0; e < DPL; e += 4) {
+    const float4 v = live ? *reinterpret_cast<const float4*>(mine + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[e] = v.x; S[e + 1] = v.y; S[e + 2] = v.z; S[e + 3] = v.w;
+  }
+  const int n_runs = (last - first + run - 1) / run;
+  issue(0, 0);
+  for (int c = 0; c < n_runs; ++c) {
+    if (c + 1 < n_runs) {
+      issue(c + 1, (c + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const float* k_s = gdn_stage + (size_t)(c & 1) * per;
+    const float* q_s = k_s + run * dim_p;
+    const float* v_s = q_s + run * dim_p;
+    const float* b_s = v_s + run * cols;
+    const float* g_s = b_s + run;
+    const int t0 = first + c * run;
+    const int n = min(run, last - t0);
+    for (int tok = 0; tok < n; ++tok) {
+      float kk[DPL], qq[DPL];
+#pragma unroll
+      for (int e = 0; e < DPL; e += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(k_s + tok * dim_p + part * DPL + e);
+        const float4 b = *reinterpret_cast<const float4*>(q_s + tok * dim_p + part * DPL + e);
+        kk[e] = a.x; kk[e + 1] = a.y; kk[e + 2] = a.z; kk[e + 3] = a.w;
+        qq[e] = b.x; qq[e + 1] = b.y; qq[e + 2] = b.z; qq[e + 3] = b.w;
+      }
+      const float vj = v_s[tok * cols + col], beta = b_s[tok], decay = g_s[tok];
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) dot = fmaf(S[e], kk[e], dot);
+      for (int o = P >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = beta * (vj - decay * dot);
+      float out = 0.f;
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) {
+        S[e] = fmaf(kk[e], u, decay * S[e]);
+        out = fmaf(S[e], qq[e], out);
+      }
+      for (int o = P >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      if (live && part == 0) o_out[(size_t)(t0 + tok) * heads * vdim + h * vdim + j] = out;
+    }
+    __syncthreads();      // the buffer is filled again two runs on
+  }
+  if (live) {
+#pragma unroll
+    for (int e = 0; e < DPL; e += 4)
+      *reinterpret_cast<float4*>(mine + e) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
+  }
+}
+
+template <typename TG, typename TO>
+__global__ void gdn_out_norm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, int ld, int g_at,
+                                    const float* __restrict__ gain, float scale, float eps, TO* __restrict__ out,
+                                    int n_rows, int heads, int vdim, const int* __restrict__ row_req) {
+  pdl_wait();
+  pdl_launch();
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= n_rows * heads) return;
+  const int t = unit / heads, h = unit % heads;
+  if (row_req[t] < 0) return;
+  const float* row = o + ((size_t)t * heads + h) * vdim;
+  float ss = 0.f;
+  for (int l = lane; l < vdim; l += 32) ss += row[l] * row[l];
+  ss = warp_sum(ss);
+  const float inv = (1.0f / sqrtf(ss / (float)vdim + eps)) * scale;
+  const TG* gates = gate + (size_t)t * ld + g_at + h * vdim;
+  TO* y = out + ((size_t)t * heads + h) * vdim;
+  for (int l = lane; l < vdim; l += 32) {
+    const float z = to_float(gates[l]);
+    y[l] = from_float<TO>(row[l] * inv * gain[l] * (z * gdn_sigmoid(z)));
+  }
+}
+
+// ---- launchers -----------------------------------------------------------------------------------
+static inline int gdn_parts(int dim, int dpl) {
+  int p = 1;
+  while (p * dpl < dim) p <<= 1;
+  return p;
+}
+
+// Rows of a head's padded state column (the recurrence keeps 8 rows a thread up to dim 256, 32 beyond).
+TOKB200_API int tokb200_gdn_padded_dim(int dim) {
+  if (dim <= 0 || dim > 1024) return 0;
+  const int dpl = dim <= 256 ? 8 : 32;
+  return gdn_parts(dim, dpl) * dpl;
+}
+
+TOKB200_API int tokb200_gdn_prepare(const void* proj, int proj_dtype, int ld, int qkv_at, int b_at, int a_at,
+                                    int groups, int heads, int dim, int vdim, int taps, const float* conv_w,
+                                    const float* a_log, const float* dt_bias, float* state, long long state_stride,
+                                    int conv_off, const int* row_req, const int* q_start, const int* state_slot,
+                                    int n_rows, int n_requests, float* qkv_out, float* bg_out, cudaStream_t stream) {
+  if (n_rows <= 0 || n_requests <= 0) return TOKB200_OK;
+  if (groups <= 0 || heads <= 0 || heads % groups || dim <= 0 || vdim <= 0 || taps < 1 || taps > GDN_MAX_TAPS ||
+      n_requests > 65535)
+    return TOKB200_BAD_SIZE;
+  const int channels = 2 * groups * dim + heads * vdim;
+  const size_t smem = (size_t)channels * sizeof(float);
+  if (smem > 48 * 1024) return TOKB200_BAD_SIZE;
+  const float q_scale = 1.0f / sqrtf((float)dim);
+  int status;
+  if (proj_dtype == TOKB200_F32)
+    status = launch_dependent(gdn_prepare_kernel<float>, dim3(n_rows), dim3(GDN_THREADS), smem, stream,
+                              (const float*)proj, ld, qkv_at, b_at, a_at, groups, heads, dim, vdim, taps, conv_w, a_log,
+                              dt_bias, (const float*)state, state_stride, conv_off, row_req, q_start, state_slot,
+                              q_scale, qkv_out, bg_out);
+  else if (proj_dtype == TOKB200_BF16)
+    status = launch_dependent(gdn_prepare_kernel<__nv_bfloat16>, dim3(n_rows), dim3(GDN_THREADS), smem, stream,
+                              (const __nv_bfloat16*)proj, ld, qkv_at, b_at, a_at, groups, heads, dim, vdim, taps,
+                              conv_w, a_log, dt_bias, (const float*)state, state_stride, conv_off, row_req, q_start,
+                              state_slot, q_scale, qkv_out, bg_out);
+  else
+    return TOKB200_BAD_DTYPE;
+  if (status != TOKB200_OK || taps == 1) return status;
+  dim3 grid((channels + 127) / 128, n_requests);
+  if (proj_dtype == TOKB200_F32)
+    return launch_dependent(gdn_conv_state_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, ld, qkv_at,
+                            channels, taps, state, state_stride, conv_off, q_start, state_slot);
+  return launch_dependent(gdn_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
+                          (const __nv_bfloat16*)proj, ld, qkv_at, channels, taps, state, state_stride, conv_off,
+                          q_start, state_slot);
+}
+
+TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, int heads, int dim, int vdim,
+                                 float* state, long long state_stride, const int* q_start, const int* state_slot,
+                                 int n_requests, float* o_out, cudaStream_t stream) {
+  if (n_requests <= 0) return TOKB200_OK;
+  if (groups <= 0 || heads <= 0 || heads % groups || dim <= 0 || dim > 1024 || vdim <= 0 || heads > 65535 ||
+      n_requests > 65535)
+    return TOKB200_BAD_SIZE;
+  if (((uintptr_t)state & 15) || state_stride % 4) return TOKB200_BAD_ALIGNMENT;
+  const int channels = 2 * groups * dim + heads * vdim;
+  const int dpl = dim <= 256 ? 8 : 32;
+  const int P = gdn_parts(dim, dpl);
+  const int cols = GDN_THREADS / P;
+  const int dim_p = P * dpl;
+  // tokens a run: what two buffers of 48 KB together hold, at most 16
+  int run = (48 * 1024 / 2 / (int)sizeof(float)) / (2 * dim_p + cols + 2);
+  run = run > 16 ? 16 : run;
+  if (run < 1) return TOKB200_BAD_SIZE;
+  const size_t smem = (size_t)2 * run * (2 * dim_p + cols + 2) * sizeof(float);
+  dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
+  if (dpl == 8)
+    return launch_dependent(gdn_scan_kernel<8>, grid, dim3(GDN_THREADS), smem, stream, qkv, bg, channels, groups,
+                            heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out);
+  return launch_dependent(gdn_scan_kernel<32>, grid, dim3(GDN_THREADS), smem, stream, qkv, bg, channels, groups,
+                          heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out);
+}
+
+TOKB200_API int tokb200_gdn_out_norm(const float* o, const void* gate, int gate_dtype, int ld, int g_at,
+                                     const float* gain, float scale, float eps, void* out, int out_dtype, int n_rows,
+                                     int heads, int vdim, const int* row_req, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (heads <= 0 || vdim <= 0) return TOKB200_BAD_SIZE;
+  const long long units = (long long)n_rows * heads;
+  dim3 grid((unsigned)((units + 7) / 8)), block(256);
+#define LAUNCH(TG, TO)                                                                                       \
+  return launch_dependent(gdn_out_norm_kernel<TG, TO>, grid, block, 0, stream, o, (const TG*)gate, ld, g_at, \
+                          gain, scale, eps, (TO*)out, n_rows, heads, vdim, row_req)
+  if (gate_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
+  if (gate_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  if (gate_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (gate_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return TOKB200_BAD_DTYPE;
+}

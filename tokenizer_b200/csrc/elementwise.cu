@@ -7,11 +7,11 @@
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------
-// embedding gather: x[t, :] = table[ids[t], :], widened to 32-bit
+// embedding gather: x[t, :] = table[ids[t], :] * scale, widened to 32-bit
 // ----------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ x, int hidden, int vocab) {
+                             float* __restrict__ x, int hidden, int vocab, float scale) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
@@ -19,18 +19,18 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
   if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read outside
   const T* row = table + (size_t)id * hidden;
   float* out = x + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]) * scale;
 }
 
 TOKB200_API int tokb200_embed(const int* ids, const void* table, int table_dtype, float* x,
-                              int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+                              int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
   if (n_tokens <= 0) return TOKB200_OK;
   if (table_dtype == TOKB200_F32)
     return launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, ids,
-                            (const float*)table, x, hidden, vocab);
+                            (const float*)table, x, hidden, vocab, scale);
   if (table_dtype == TOKB200_BF16)
     return launch_dependent(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, ids,
-                            (const __nv_bfloat16*)table, x, hidden, vocab);
+                            (const __nv_bfloat16*)table, x, hidden, vocab, scale);
   return TOKB200_BAD_DTYPE;
 }
 

@@ -1,0 +1,116 @@
+// A feed-forward of routed experts, computed as ONE gated feed-forward whose inner lanes are the
+// experts' lanes side by side (and a shared expert's behind them): every inner lane is scaled by its
+// expert's share for the token, which is zero for an expert the token did not choose, so the down
+// product over all lanes is the weighted sum of the chosen experts' outputs.
+//
+//   moe_route   the router's logits (32-bit sums; one more row for the shared expert's gate), then
+//               share[t, e] = softmax over the `top` largest logits of token t (ties: the lower
+//               index), zero elsewhere; share[t, experts] = sigmoid(the shared expert's gate logit)
+//   moe_gate    act[t, c] = f(gate[t, c]) * up[t, c] * share[t, expert of lane c], f the activation
+#include "common.cuh"
+
+#define MOE_MAX_EXPERTS 1024
+
+// h: the feed-forward's input [T, hidden] (float32, or its bfloat16 rounding); w: float32
+// [experts + shared, hidden], the router's rows and behind them the shared expert's gate row.
+// A block a token: its warps take the logits in turn (32-bit sums), thread 0 then chooses.
+template <typename TI>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TI* __restrict__ h, const float* __restrict__ w, int hidden, int experts, int top,
+                 int shared, float* __restrict__ share) {
+  __shared__ float z[MOE_MAX_EXPERTS + 1];
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TI* row = h + (size_t)t * hidden;
+  for (int e = warp; e < experts + shared; e += blockDim.x >> 5) {
+    const float* we = w + (size_t)e * hidden;
+    float acc = 0.f;
+    for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(row[i]), we[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncthreads();
+  float* out = share + (size_t)t * (experts + shared);
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) out[e] = 0.f;
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  unsigned taken[MOE_MAX_EXPERTS / 32];
+  for (int i = 0; i < (experts + 31) / 32; ++i) taken[i] = 0u;
+  float highest = 0.f, sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    int best = -1;
+    float value = -INFINITY;
+    for (int e = 0; e < experts; ++e) {
+      if (!((taken[e >> 5] >> (e & 31)) & 1u) && (best < 0 ? z[e] == z[e] : z[e] > value)) {
+        best = e;
+        value = z[e];
+      }
+    }
+    if (best < 0) break;
+    taken[best >> 5] |= 1u << (best & 31);
+    if (k == 0) highest = value;
+    const float weight = expf(value - highest);
+    out[best] = weight;
+    sum += weight;
+  }
+  for (int e = 0; e < experts; ++e)
+    if ((taken[e >> 5] >> (e & 31)) & 1u) out[e] /= sum;
+  if (shared) out[experts] = 1.0f / (1.0f + expf(-z[experts]));
+}
+
+// gu: [T, 2 I], gates in the first I columns, ups in the last; lanes 0 .. experts * ff belong to the
+// routed experts (ff lanes each), the lanes behind to the shared expert.
+template <typename T>
+__global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restrict__ share, T* __restrict__ out,
+                                int inner, int experts, int ff, int shared, int act, size_t n) {
+  pdl_wait();
+  pdl_launch();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const size_t t = i / inner;
+    const int c = (int)(i % inner);
+    const int e = c < experts * ff ? c / ff : experts;
+    const float w = share[t * (experts + shared) + e];
+    float value = 0.f;
+    if (w != 0.f) {
+      const float g = to_float(gu[t * 2 * inner + c]), u = to_float(gu[t * 2 * inner + inner + c]);
+      value = gate_activation(act, g) * u * w;
+    }
+    out[i] = from_float<T>(value);
+  }
+}
+
+TOKB200_API int tokb200_moe_route(const void* h, int h_dtype, const float* w, int hidden, int experts, int top,
+                                  int shared, float* share, int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (hidden <= 0 || experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts ||
+      (shared != 0 && shared != 1))
+    return TOKB200_BAD_SIZE;
+  if (h_dtype == TOKB200_F32)
+    return launch_dependent(moe_route_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (const float*)h, w, hidden,
+                            experts, top, shared, share);
+  if (h_dtype == TOKB200_BF16)
+    return launch_dependent(moe_route_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, stream,
+                            (const __nv_bfloat16*)h, w, hidden, experts, top, shared, share);
+  return TOKB200_BAD_DTYPE;
+}
+
+TOKB200_API int tokb200_moe_gate(const void* gu, const float* share, void* out, int dtype, int n_rows, int inner,
+                                 int experts, int ff, int shared, int act, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (inner <= 0 || experts <= 0 || ff <= 0 || (long long)experts * ff > inner || act < 0 || act >= TOKB200_ACT_COUNT ||
+      (!shared && (long long)experts * ff != inner))
+    return TOKB200_BAD_SIZE;
+  const size_t n = (size_t)n_rows * inner;
+  const size_t blocks = (n + 255) / 256;
+  const dim3 grid((unsigned)(blocks < 8192 ? blocks : 8192));
+  if (dtype == TOKB200_F32)
+    return launch_dependent(moe_gate_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, share, (float*)out,
+                            inner, experts, ff, shared, act, n);
+  if (dtype == TOKB200_BF16)
+    return launch_dependent(moe_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                            share, (__nv_bfloat16*)out, inner, experts, ff, shared, act, n);
+  return TOKB200_BAD_DTYPE;
+}

@@ -1,0 +1,80 @@
+// Queries, keys and values of an attention layer whose key and value heads differ in size, from one
+// stacked product: the projection's bias, the rotation of the leading `rot_dims` lanes of every query
+// and key head in the interleaved form (lane 2i pairs with lane 2i + 1; the pair (u, v) at position p
+// becomes (u cos a - v sin a, v cos a + u sin a), a = float32(p) * inv_freq[i]), and the write of the
+// token's keys and values into its cache slot.  Cache rows and query rows have `row` lanes a head,
+// row >= max(dim, vdim): keys and queries fill the first `dim` lanes, values the first `vdim`, the
+// rest is written as zero, so that kernels which take one head size serve both.
+//
+// proj: [T, ld]; columns at .. : q (heads * dim), k (kv_heads * dim), v (kv_heads * vdim).
+// bias: float32, indexed like proj's columns from `at` on (or null).  A block a token.
+#include "common.cuh"
+
+template <typename TI, typename T>
+__global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int at, const float* __restrict__ bias,
+                                        const float* __restrict__ inv_freq, int rot_dims,
+                                        const int* __restrict__ pos, const int* __restrict__ slot,
+                                        const int* __restrict__ row_req, T* __restrict__ q_out,
+                                        T* __restrict__ k_pool, T* __restrict__ v_pool, int heads, int kv_heads,
+                                        int dim, int vdim, int row) {
+  const int t = blockIdx.x;
+  const int r = row_req[t];
+  const int p = pos[t];
+  const int where = slot ? slot[t] : -1;
+  pdl_wait();
+  pdl_launch();
+  if (r < 0) return;
+  const TI* in = proj + (size_t)t * ld + at;
+  const int lanes = (heads + 2 * kv_heads) * row;
+  for (int i = threadIdx.x; i < lanes; i += blockDim.x) {
+    const int head = i / row, l = i % row;
+    if (head < heads + kv_heads) {                       // a query or key head: bias, rotation
+      float value = 0.f;
+      if (l < dim) {
+        const int col = head * dim + l;
+        value = to_float(in[col]) + (bias ? bias[col] : 0.f);
+        if (l < rot_dims) {
+          const int mate = col ^ 1;
+          const float other = to_float(in[mate]) + (bias ? bias[mate] : 0.f);
+          float s, c;
+          sincosf((float)p * inv_freq[l >> 1], &s, &c);
+          value = (l & 1) ? value * c + other * s : value * c - other * s;
+        }
+      }
+      if (head < heads) {
+        q_out[((size_t)t * heads + head) * row + l] = from_float<T>(value);
+      } else if (where >= 0) {
+        k_pool[((size_t)where * kv_heads + (head - heads)) * row + l] = from_float<T>(value);
+      }
+    } else if (where >= 0) {
+      const int g = head - heads - kv_heads;
+      float value = 0.f;
+      if (l < vdim) {
+        const int col = (heads + kv_heads) * dim + g * vdim + l;
+        value = to_float(in[col]) + (bias ? bias[col] : 0.f);
+      }
+      v_pool[((size_t)where * kv_heads + g) * row + l] = from_float<T>(value);
+    }
+  }
+}
+
+TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int ld, int at, const float* bias,
+                                         const float* inv_freq, int rot_dims, const int* pos, const int* slot,
+                                         const int* row_req, void* q_out, void* k_pool, void* v_pool,
+                                         int out_dtype, int n_rows, int heads, int kv_heads, int dim, int vdim,
+                                         int row, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
+      rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr))
+    return TOKB200_BAD_SIZE;
+#define LAUNCH(TI, T)                                                                                         \
+  return launch_dependent(qkv_rotate_store_kernel<TI, T>, dim3(n_rows), dim3(256), 0, stream, (const TI*)proj, \
+                          ld, at, bias, inv_freq, rot_dims, pos, slot, row_req, (T*)q_out, (T*)k_pool,        \
+                          (T*)v_pool, heads, kv_heads, dim, vdim, row)
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return TOKB200_BAD_DTYPE;
+}

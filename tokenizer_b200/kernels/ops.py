@@ -201,11 +201,12 @@ def raise_if_error(where: str = "") -> None:
 
 
 # --------------------------------------------------------------------------- #
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale, float32."""
     n, hidden = out.shape
     _check(_lib("elementwise").tokb200_embed(
         _ptr(ids), _ptr(table), _i(_tag(table)), _ptr(out), _i(n), _i(hidden),
-        _i(table.shape[0]), _stream()), "embed")
+        _i(table.shape[0]), _f(scale), _stream()), "embed")
 
 
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
@@ -314,8 +315,9 @@ def _sink(sink, nh):
 
 
 def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page,
-                            window, scale, sink: Optional[torch.Tensor] = None) -> None:
-    """`sink` (float32, one per query head): a score without key or value that counts once in
+                            window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
+    """`chunk` (optional): keys are seen inside chunks of that many positions counted from 0 (a
+    query sees the keys of its own chunk up to itself).  `sink` (float32, one per query head): a score without key or value that counts once in
     the softmax's denominator, unscaled.  `v_pool` may be `k_pool` itself (values that are the
     leading lanes of the key rows)."""
     if d > 1024:
@@ -325,7 +327,7 @@ def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, n
     _check(_lib("attention_generic").tokb200_paged_attention_generic(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _i(_tag(q)), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(q.shape[0]), _i(nh), _i(nkv),
-        _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _sink(sink, nh), _stream()),
+        _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh), _stream()),
         "paged_attention")
 
 
@@ -388,7 +390,8 @@ def decode_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page, window,
-                     scale, rows: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> None:
+                     scale, rows: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+                     chunk: Optional[int] = None) -> None:
     """Attention for rows of one token each (bfloat16): keys are split over
     blocks and merged; the scratch for the pieces is kept per (device, rows,
     heads, head size) and reused by every layer, which run one after another.  With `rows`
@@ -410,7 +413,7 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
     _check(lib.tokb200_decode_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
-        _i(page), _i(-1 if window is None else int(window)), _f(scale), _ptr(scratch),
+        _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _ptr(scratch),
         _ptr(counters), _ptr(rows), _sink(sink, nh), _stream()), "decode_attention")
 
 
@@ -539,7 +542,7 @@ def prefill_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv,
-                      d, page, window, scale, sink: Optional[torch.Tensor] = None) -> None:
+                      d, page, window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
     """Attention for portions of prompts (bfloat16).  `tiles` is int32 [n, 2]:
     (first row, rows <= 64) of consecutive rows of one request."""
     if q.dtype != torch.bfloat16:
@@ -550,7 +553,7 @@ def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
     _check(lib.tokb200_prefill_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
-        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _sink(sink, nh),
+        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh),
         _stream()), "prefill_attention")
 
 
@@ -784,7 +787,7 @@ def attention_tcgen05_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv, d,
-                      page, window, scale, sink: Optional[torch.Tensor] = None) -> None:
+                      page, window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
     """Attention for portions of prompts on tcgen05 (bfloat16, head size 64 or 128).
     `tiles` is int32 [n, 2]: (first row, rows <= 128) of consecutive rows of one request."""
     if q.dtype != torch.bfloat16:
@@ -795,7 +798,7 @@ def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
     _check(lib.tokb200_attention_tcgen05(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
-        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _sink(sink, nh),
+        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh),
         _stream()), "attention_tcgen05")
 
 
@@ -1093,6 +1096,162 @@ def rotate_interleaved(x: torch.Tensor, heads: int, lane0: int, dims: int, inv_f
     _check(_lib("latent").tokb200_rotate_interleaved(
         _ptr(x), _i(_tag(x)), _i(heads), _i(width // heads), _i(lane0), _i(dims), _ptr(inv_freq), _ptr(pos),
         _ptr(row_req), _i(n_rows), _stream()), "rotate_interleaved")
+
+
+# ---- layer norm, the stream's steps around normed sublayer outputs ----
+def layer_norm(x: torch.Tensor, gain: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+               rows: Optional[torch.Tensor] = None) -> None:
+    """out = (x - mean) / sqrt(var + eps) * gain + bias over the last axis of x (float32 [T, H]); with
+    `rows` (int32) only those rows are read and `out` is dense [len(rows), H]."""
+    hidden = x.shape[-1]
+    if x.dtype != torch.float32 or gain.dtype != torch.float32 or bias.dtype != torch.float32 or \
+            gain.numel() != hidden or bias.numel() != hidden or out.shape[-1] != hidden:
+        raise ValueError("layer_norm: x, gain and bias are float32 of one width")
+    _check(_lib("layer_norm").tokb200_layer_norm(
+        _ptr(x), _ptr(gain), _ptr(bias), _ptr(out), _i(_tag(out)), _ptr(rows), _i(out.shape[0]), _i(hidden),
+        _f(eps), _stream()), "layer_norm")
+
+
+def _term(term, like):
+    """(pointer, dtype tag, partial sums, their distance, scale) of one scaled term of a sublayer's
+    output: (tensor [T, H] or float32 partial sums [S, T, H], scale), or None."""
+    if term is None:
+        return [_ptr(None), _i(F32), _i(1), _ll(0), _f(0.0)]
+    y, scale = term
+    n_partials, stride = _partials(y, like)
+    return [_ptr(y), _i(_tag(y)), _i(n_partials), _ll(stride), _f(scale)]
+
+
+def post_norm_add(x: torch.Tensor, terms, gain, bias, eps: float, next_gain=None, next_bias=None,
+                  next_eps: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
+    """x += LN(sum of the scaled terms) * gain + bias in place (x float32 [T, H]; `terms`: one or two
+    (tensor, scale)); with `out`, also out = LN(x) * next_gain + next_bias of the new x."""
+    n_rows, hidden = x.shape
+    if x.dtype != torch.float32 or not 1 <= len(terms) <= 2 or gain.numel() != hidden or bias.numel() != hidden:
+        raise ValueError("post_norm_add: x float32 [T, H], one or two terms, gain and bias of H")
+    if out is not None and (next_gain is None or next_bias is None or tuple(out.shape) != (n_rows, hidden)):
+        raise ValueError("post_norm_add: the norm behind the add needs gain, bias and out [T, H]")
+    args = _term(terms[0], x) + _term(terms[1] if len(terms) > 1 else None, x)
+    _check(_lib("layer_norm").tokb200_post_norm_add(
+        _ptr(x), *args, _ptr(gain), _ptr(bias), _f(eps), _ptr(next_gain), _ptr(next_bias), _f(next_eps),
+        _ptr(out), _i(_tag(out) if out is not None else F32), _i(n_rows), _i(hidden), _stream()), "post_norm_add")
+
+
+def scaled_sum(terms, out: torch.Tensor) -> None:
+    """out (float32 [T, H]) = sum of one or two scaled terms ((tensor or partial sums, scale))."""
+    if out.dtype != torch.float32 or not 1 <= len(terms) <= 2:
+        raise ValueError("scaled_sum: out is float32, one or two terms")
+    args = _term(terms[0], out) + _term(terms[1] if len(terms) > 1 else None, out)
+    _check(_lib("layer_norm").tokb200_scaled_sum(*args, _ptr(out), _ll(out.numel()), _stream()), "scaled_sum")
+
+
+def stream_inject(x: torch.Tensor, other: Optional[torch.Tensor], vector: Optional[torch.Tensor]) -> None:
+    """x[t] += other[t] + vector, each where given (float32)."""
+    n_rows, hidden = x.shape
+    if x.dtype != torch.float32 or (other is not None and (other.dtype != torch.float32 or other.shape != x.shape)) or \
+            (vector is not None and (vector.dtype != torch.float32 or vector.numel() != hidden)):
+        raise ValueError("stream_inject: float32 [T, H] and a float32 vector of H")
+    _check(_lib("layer_norm").tokb200_stream_inject(_ptr(x), _ptr(other), _ptr(vector), _i(n_rows), _i(hidden),
+                                                    _stream()), "stream_inject")
+
+
+# ---- the gated delta rule ----
+def gdn_padded_dim(dim: int) -> int:
+    """Rows of a head's state column as the recurrence keeps it (dim rounded up to what its threads
+    hold: whole 8s times a power of two up to 256, whole 32s beyond); 0: a size it does not take."""
+    if not 0 < dim <= 1024:
+        return 0
+    per = 8 if dim <= 256 else 32
+    parts = 1
+    while parts * per < dim:
+        parts *= 2
+    return parts * per
+
+
+def gdn_prepare(proj: torch.Tensor, qkv_at: int, b_at: int, a_at: int, groups: int, heads: int, dim: int, vdim: int,
+                taps: int, conv_w, a_log, dt_bias, state: torch.Tensor, conv_off: int, row_req, q_start, state_slot,
+                qkv_out: torch.Tensor, bg_out: torch.Tensor) -> None:
+    """Short convolution + silu of q, k, v (from `proj`'s columns qkv_at ..), unit vectors for q (times
+    dim^-1/2) and k, beta = sigmoid(proj[b_at ..]) and the decay exp(-exp(a_log) softplus(proj[a_at ..] +
+    dt_bias)) -> `qkv_out` float32 [T, channels], `bg_out` float32 [T, 2 heads]; then the convolution's
+    kept inputs in `state` (float32 [slots, n], at `conv_off` in a slot) move on by the step's rows."""
+    channels = 2 * groups * dim + heads * vdim
+    n = proj.shape[0]
+    if state.dtype != torch.float32 or state.dim() != 2 or tuple(qkv_out.shape) != (n, channels) or \
+            tuple(bg_out.shape) != (n, 2 * heads) or qkv_out.dtype != torch.float32 or bg_out.dtype != torch.float32 or \
+            conv_w.numel() != channels * taps or conv_off + (taps - 1) * channels > state.shape[1]:
+        raise ValueError("gdn_prepare: sizes of the state, the taps or the outputs disagree")
+    _check(_lib("delta_rule").tokb200_gdn_prepare(
+        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(qkv_at), _i(b_at), _i(a_at), _i(groups), _i(heads), _i(dim),
+        _i(vdim), _i(taps), _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), _ptr(state), _ll(state.shape[1]), _i(conv_off),
+        _ptr(row_req), _ptr(q_start), _ptr(state_slot), _i(n), _i(q_start.shape[0] - 1), _ptr(qkv_out), _ptr(bg_out),
+        _stream()), "gdn_prepare")
+
+
+def gdn_scan(qkv: torch.Tensor, bg: torch.Tensor, groups: int, heads: int, dim: int, vdim: int, state: torch.Tensor,
+             q_start, state_slot, o_out: torch.Tensor) -> None:
+    """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over every request's rows,
+    head by head; `state` float32 [slots, n] holds the heads' matrices transposed and padded
+    ([heads, vdim, gdn_padded_dim(dim)]) at the start of a slot; `o_out` float32 [T, heads * vdim]."""
+    n = qkv.shape[0]
+    if state.dtype != torch.float32 or o_out.dtype != torch.float32 or tuple(o_out.shape) != (n, heads * vdim) or \
+            qkv.shape[1] != 2 * groups * dim + heads * vdim or heads * vdim * gdn_padded_dim(dim) > state.shape[1]:
+        raise ValueError("gdn_scan: sizes of the state or the outputs disagree")
+    _check(_lib("delta_rule").tokb200_gdn_scan(
+        _ptr(qkv), _ptr(bg), _i(groups), _i(heads), _i(dim), _i(vdim), _ptr(state), _ll(state.shape[1]),
+        _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _ptr(o_out), _stream()), "gdn_scan")
+
+
+def gdn_out_norm(o: torch.Tensor, gate: torch.Tensor, g_at: int, gain: torch.Tensor, scale: float, eps: float,
+                 out: torch.Tensor, heads: int, vdim: int, row_req) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * gain * scale * silu(gate[t, g_at + h vdim ..])."""
+    n = o.shape[0]
+    if o.dtype != torch.float32 or tuple(o.shape) != (n, heads * vdim) or tuple(out.shape) != (n, heads * vdim) or \
+            gain.numel() != vdim or g_at + heads * vdim > gate.shape[1]:
+        raise ValueError("gdn_out_norm: o float32 [T, heads * vdim], a gain of vdim, the gate's columns inside its matrix")
+    _check(_lib("delta_rule").tokb200_gdn_out_norm(
+        _ptr(o), _sliced_ptr(gate), _i(_tag(gate)), _i(_ld(gate)), _i(g_at), _ptr(gain), _f(scale), _f(eps), _ptr(out),
+        _i(_tag(out)), _i(n), _i(heads), _i(vdim), _ptr(row_req), _stream()), "gdn_out_norm")
+
+
+# ---- queries, keys and values with unlike head sizes; routed experts ----
+def qkv_rotate_store(proj: torch.Tensor, at: int, bias, inv_freq, rot_dims: int, pos, slot, row_req, q_out, k_pool,
+                     v_pool, heads: int, kv_heads: int, dim: int, vdim: int, row: int) -> None:
+    """Bias, interleaved rotation of the first `rot_dims` lanes of every query and key head, and the
+    cache write, from `proj`'s columns at .. (q, k, v); rows of `row` lanes a head, zero behind dim
+    (queries, keys) and vdim (values).  `slot` None: no cache write."""
+    n = proj.shape[0]
+    if tuple(q_out.shape) != (n, heads * row) or k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype or \
+            at + heads * dim + kv_heads * (dim + vdim) > proj.shape[1]:
+        raise ValueError("qkv_rotate_store: q_out is [T, heads * row] in the cache's type, the columns inside proj")
+    _check(_lib("rotary_store").tokb200_qkv_rotate_store(
+        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(at), _ptr(bias), _ptr(inv_freq), _i(rot_dims), _ptr(pos),
+        _ptr(slot), _ptr(row_req), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _i(_tag(q_out)), _i(n), _i(heads),
+        _i(kv_heads), _i(dim), _i(vdim), _i(row), _stream()), "qkv_rotate_store")
+
+
+def moe_route(h: torch.Tensor, w: torch.Tensor, experts: int, top: int, shared: bool, share: torch.Tensor) -> None:
+    """Router logits z = w h in 32-bit (`w` float32 [experts (+ 1), hidden]; `h` float32 or bfloat16), then
+    share[t, e] = softmax over token t's `top` largest logits, zero for the other experts; with
+    `shared`, share[t, experts] = sigmoid(z[t, experts])."""
+    n, hidden = h.shape
+    rows = experts + int(shared)
+    if w.dtype != torch.float32 or tuple(w.shape) != (rows, hidden) or share.dtype != torch.float32 or \
+            tuple(share.shape) != (n, rows):
+        raise ValueError("moe_route: float32 router rows [experts (+ 1), hidden], shares float32 [T, experts (+ 1)]")
+    _check(_lib("moe").tokb200_moe_route(_ptr(h), _i(_tag(h)), _ptr(w), _i(hidden), _i(experts), _i(top),
+                                         _i(int(shared)), _ptr(share), _i(n), _stream()), "moe_route")
+
+
+def moe_gate(gu: torch.Tensor, share: torch.Tensor, out: torch.Tensor, experts: int, ff: int, shared: bool,
+             activation: str = "silu") -> None:
+    """out[t, c] = act(gu[t, c]) * gu[t, I + c] * share[t, expert of lane c]: lanes 0 .. experts * ff
+    are the routed experts' (ff each), the lanes behind the shared expert's."""
+    n, inner = out.shape
+    if gu.shape[1] != 2 * inner or gu.dtype != out.dtype or tuple(share.shape) != (n, experts + int(shared)):
+        raise ValueError("moe_gate: input [T, 2 I], output [T, I] of one type, shares [T, experts (+ 1)]")
+    _check(_lib("moe").tokb200_moe_gate(_ptr(gu), _ptr(share), _ptr(out), _i(_tag(gu)), _i(n), _i(inner), _i(experts),
+                                        _i(ff), _i(int(shared)), _i(activation_tag(activation)), _stream()), "moe_gate")
 
 
 # ---- read-only streams in the decoding kernels' access patterns (bench.py --stream-probe) ----

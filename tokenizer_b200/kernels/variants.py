@@ -20,6 +20,10 @@ def all_variants():
         ("recurrence.cu", (), ()),
         ("activation.cu", (), ()),
         ("latent.cu", (), ()),
+        ("layer_norm.cu", (), ()),
+        ("delta_rule.cu", (), ()),
+        ("rotary_store.cu", (), ()),
+        ("moe.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -133,11 +133,12 @@ class PagedAttention:
     """What every mixer that attends over the paged cache shares: the annotations its kernels
     want packed with a step, the kernel choice (`attend`) and its say in a captured step's key.
     A mixer that inherits it sets `nh` (query heads), `nkv` (heads of the cache rows), `d` (lanes
-    of a cache row's head), `window` (None: all keys), `scale` and, where its softmax has one,
+    of a cache row's head), `window` (None: all keys), `chunk` (None: no chunks), `scale` and, where its softmax has one,
     `sink` (float32, one learned score per query head that counts once in the denominator)."""
 
     graph_safe = True   # launches depend on device-side metadata only
     sink = None
+    chunk = None        # n: keys are seen inside chunks of n positions counted from 0
 
     def batch_annotations(self):
         return [_TILES, _WIDE_TILES, _LONG_TILES, _LONG_WIDE_TILES, _SINGLES]
@@ -163,7 +164,7 @@ class PagedAttention:
                 ops.decode_attention_supported(self.nh, self.nkv, self.d):
             ops.decode_attention(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink)
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink, chunk=self.chunk)
             return
         wide, tiles = ctx.views.get(_WIDE_TILES.key), ctx.views.get(_TILES.key)
         singles = ctx.views.get(_SINGLES.key)
@@ -174,7 +175,7 @@ class PagedAttention:
             # (keys split over blocks, the group's heads as one tile), the portions to theirs
             ops.decode_attention(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0], sink=sink)
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0], sink=sink, chunk=self.chunk)
             wide, tiles = ctx.views[_LONG_WIDE_TILES.key], ctx.views[_LONG_TILES.key]
         if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
                 wide is not None and ctx.max_q_len >= _WIDE_FROM and \
@@ -183,18 +184,18 @@ class PagedAttention:
             ops.attention_tcgen05(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 wide[0], wide[1], self.nh, self.nkv, self.d, group.page_size,
-                self.window, self.scale, sink=sink)
+                self.window, self.scale, sink=sink, chunk=self.chunk)
             return
         if q.dtype == torch.bfloat16 and tiles is not None and \
                 ops.prefill_attention_supported(self.nh, self.nkv, self.d):
             ops.prefill_attention(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 tiles[0], tiles[1], self.nh, self.nkv, self.d, group.page_size,
-                self.window, self.scale, sink=sink)
+                self.window, self.scale, sink=sink, chunk=self.chunk)
             return
         ops.paged_attention_generic(
             q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink)
+            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink, chunk=self.chunk)
 
 
 class GQAttention(PagedAttention):
@@ -358,4 +359,93 @@ class GQAttention(PagedAttention):
         return self.out.forward(mixed, partials_ok=True)
 
 
+class RotaryGQAttention(PagedAttention):
+    """Grouped-query attention whose key and value heads may differ in size, with biases, a score
+    scale of its own and the interleaved rotation on the leading lanes of every query and key head:
+    q = Wq h + bq (heads x dim), k = Wk h + bk (kv_heads x dim), v = Wv h + bv (kv_heads x vdim);
+    score = q . k * scale; softmax over the keys the query sees (all earlier ones, those inside
+    `window`, or those of its own chunk of `chunk` positions counted from the sequence's start);
+    Wo on the heads' outputs (heads x vdim).  Tensors `<prefix>.q`, `.k`, `.v` (+ `.b` with
+    `bias`), `.o`.
+
+    Cache rows and query rows have `row` lanes a head, max(dim, vdim) rounded up to whole 16s: keys
+    and queries fill the first dim lanes, values the first vdim, zeros behind (a zero lane adds
+    nothing to a score; a zero value lane meets a zero column of the padded Wo), so that the paged
+    kernels, which take one head size, serve both.  `input_stack` / `forward_projected` as for
+    the other mixers that may run side by side."""
+
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        hidden, heads, groups, dim, vdim = p["hidden_size"], p["heads"], p["kv_heads"], p["dim"], p["vdim"]
+        out = [TensorSpec(x + ".q", (heads * dim, hidden)), TensorSpec(x + ".k", (groups * dim, hidden)),
+               TensorSpec(x + ".v", (groups * vdim, hidden)), TensorSpec(x + ".o", (hidden, heads * vdim))]
+        if p.get("bias", True):
+            out += [TensorSpec(x + ".q.b", (heads * dim,)), TensorSpec(x + ".k.b", (groups * dim,)),
+                    TensorSpec(x + ".v.b", (groups * vdim,))]
+        return out
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        self.runtime = runtime
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.scale = float(p["scale"])
+        self.window, self.chunk = p.get("window"), p.get("chunk")
+        if self.nkv <= 0 or self.nh % self.nkv:
+            raise ConfigError(f"{self.nh} query heads is not a multiple of {self.nkv} kv heads")
+        if self.chunk is not None and int(self.chunk) < 1:
+            raise ConfigError("a chunk holds at least one position")
+        self.row = -(-max(self.dim, self.vdim) // 16) * 16
+        self.d = self.row
+        self.position, self.rot_dims = None, 0
+        if p.get("position") is not None:
+            self.position = build_part("position", p["position"], store, runtime)
+            self.rot_dims = int(self.position.dims)
+            if self.rot_dims > self.dim:
+                raise ConfigError(f"{self.rot_dims} rotated lanes do not fit a head of {self.dim}")
+        self._stack = [store.get(x + "." + n) for n in "qkv"]
+        self.bias = None
+        if p.get("bias", True):
+            self.bias = runtime.vector(torch.cat([store.get(x + f".{n}.b").to(torch.float32) for n in "qkv"]))
+        w_o = store.get(x + ".o")
+        if self.row != self.vdim:           # zero columns where the value lanes end
+            wide = torch.zeros((self.hidden, self.nh, self.row), dtype=w_o.dtype)
+            wide[:, :, :self.vdim] = w_o.view(self.hidden, self.nh, self.vdim)
+            w_o = wide.view(self.hidden, self.nh * self.row)
+        self.out = Linear(runtime.matrix(w_o))
+        self.inputs = None
+
+    def input_stack(self):
+        """(q, k and v matrices one under the other, as stored; nothing of their bias: the kernel
+        that rotates adds it)."""
+        return torch.cat(self._stack, dim=0), None
+
+    def cache_need(self):
+        return CacheNeed(kv=KVNeed(self.nkv, self.row, self.window, chunk=self.chunk))
+
+    def streamed_weights(self):
+        return [self.out.weight] if self.inputs is None else [self.inputs.weight, self.out.weight]
+
+    def forward_projected(self, proj, at, ctx, cache, out_scale: float = 1.0):
+        if out_scale != 1.0:
+            raise ValueError("this mixer's output is scaled by whoever adds it")
+        group = ctx.groups[cache.group]
+        q = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
+        ops.qkv_rotate_store(proj, at, self.bias, self.position.inv_freq if self.position is not None else None,
+                             self.rot_dims, ctx.pos, group.slots if cache.writes else None, ctx.row_req, q,
+                             cache.k_pool, cache.v_pool, self.nh, self.nkv, self.dim, self.vdim, self.row)
+        mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
+        self.attend(q, mixed, ctx, group, cache)
+        return self.out.forward(mixed, partials_ok=True)
+
+    def forward(self, h, ctx, cache):
+        if self.inputs is None:
+            from .recurrent import stacked_rows
+            self.inputs = Linear(self.runtime.matrix(stacked_rows([self.input_stack()[0]])))
+        return self.forward_projected(self.inputs.forward(h, out_dtype=torch.float32), 0, ctx, cache)
+
+
 register_part("mixer", "gqa_attention", GQAttention)
+register_part("mixer", "gqa_rotary", RotaryGQAttention)

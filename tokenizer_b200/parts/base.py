@@ -28,6 +28,9 @@ Interfaces (duck-typed; the classes below marked "interface" document them):
   embedding     forward(ids) -> x f32 [T,H];   head  forward(stream, rows) -> logits f32
   gate          tensors(spec); __init__(spec, store, runtime); weight, bias (a projection of a
                 sublayer's input whose sigmoid scales the sublayer's output); forward(h) -> pre
+  injection     tensors(spec); __init__(spec, store, runtime); needs_embedding (bool);
+                forward(stream, embedded) (changes the stream in front of a call of the order;
+                `embedded` is the embedding's output, kept for the parts that ask for it)
 """
 from __future__ import annotations
 
@@ -39,7 +42,7 @@ import torch
 from ..config.spec import ConfigError, PartSpec
 from ..kernels import ops
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "gate")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "gate", "injection")
 _REGISTRY: Dict[str, Dict[str, Any]] = {c: {} for c in CATEGORIES}
 
 
@@ -94,12 +97,15 @@ class Runtime:
 class KVNeed:
     """Keys and values per token: `kv_heads` x `head_dim` each (`planes` = 2), or one row of
     that size which the mixer reads as both (`planes` = 1).  With a `window`, only the last
-    window + 1 positions are ever read, and pages wholly before them are given back."""
+    window + 1 positions are ever read, and pages wholly before them are given back.  With a
+    `chunk`, a query reads the keys of its own chunk of that many positions (counted from 0) only,
+    and pages wholly before the chunk of a request's next position are given back."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2      # 2: keys and values; 1: one row a token that serves as both (a cached latent)
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -218,6 +224,15 @@ class GatedDelta:
     pre_bias: Optional[torch.Tensor]
 
 
+@dataclass
+class ScaledTerms:
+    """A mixer's output that is a sum of scaled terms (two mixers side by side): [(y, scale)], y
+    [T, H] or float32 partial sums [S, T, H].  Whoever adds it to the stream, or norms it first,
+    sums the terms in float32 on the way."""
+
+    terms: List[Tuple[torch.Tensor, float]]
+
+
 class ResidualStream:
     """The residual sum, kept in float32.  A part's output is not added at once:
     it stays pending until the next norm, which adds it while it reads the row
@@ -231,9 +246,13 @@ class ResidualStream:
         self.x = x
         self._pending: Optional[torch.Tensor] = None
         self._gated: Optional[GatedDelta] = None
+        self._normed = None      # (terms, norm): a sublayer's output that is normed before it is added
 
     @property
     def pending(self) -> Optional[torch.Tensor]:
+        if self._normed is not None:
+            (terms, post), self._normed = self._normed, None
+            post.add_to(self.x, terms)            # in place: nothing stays pending
         if self._gated is not None:
             g, self._gated = self._gated, None
             self._pending = torch.empty(self.x.shape, dtype=torch.float32, device=self.x.device)
@@ -242,11 +261,22 @@ class ResidualStream:
 
     @pending.setter
     def pending(self, value: Optional[torch.Tensor]) -> None:
-        self._pending, self._gated = value, None
+        self._pending, self._gated, self._normed = value, None, None
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta) -> None:
         self.flush()
+        if isinstance(delta, ScaledTerms):
+            summed = torch.empty(self.x.shape, dtype=torch.float32, device=self.x.device)
+            ops.scaled_sum(delta.terms, summed)
+            delta = summed
         self.pending = delta
+
+    def add_normed(self, delta, post) -> None:
+        """x += post(delta), with the norm `post` on the sublayer's OUTPUT: it stays pending, so
+        that the next norm (`normed`) can take the norm, the add and itself in one kernel.  `post`
+        offers `add_to(x, terms, then=None)`."""
+        self.flush()
+        self._normed = (delta.terms if isinstance(delta, ScaledTerms) else [(delta, 1.0)], post)
 
     def add_gated(self, delta: GatedDelta) -> None:
         self.flush()
@@ -266,6 +296,9 @@ class ResidualStream:
     GATED_NORM_ROWS = 64
 
     def normed(self, norm) -> torch.Tensor:
+        if self._normed is not None:
+            (terms, post), self._normed = self._normed, None
+            return post.add_to(self.x, terms, then=norm)
         fused = getattr(norm, "forward_gated", None)
         if self._gated is not None and fused is not None and self.x.shape[0] <= self.GATED_NORM_ROWS:
             gated, self._gated = self._gated, None

@@ -132,3 +132,63 @@ class GatedPreNormMixerOnly(GatedPreNormResidual):
 register_part("block", "gated_pre_norm_residual", GatedPreNormResidual)
 register_part("block", "gated_pre_norm_mixer_only", GatedPreNormMixerOnly)
 register_part("gate", "residual_gate", ResidualGate)
+
+
+class SandwichNormResidual:
+    """A norm in front of AND behind every sublayer: x += post1(mixer(norm1(x)));
+    x += post2(feed_forward(norm2(x))).  A sublayer's output stays pending on the stream together
+    with the norm that follows it, so that this norm, the add and the norm in front of the next
+    sublayer (of this layer or of the next) are one kernel.  A mixer may hand back a sum of scaled
+    terms (`ScaledTerms`); the norm behind it sums them."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_norm": "norm", "feed_forward_post_norm": "norm"}
+
+    def __init__(self, mixer, mixer_norm, mixer_post_norm, feed_forward=None, feed_forward_norm=None,
+                 feed_forward_post_norm=None):
+        self.mixer, self.mixer_norm, self.mixer_post_norm = mixer, mixer_norm, mixer_post_norm
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        self.feed_forward_post_norm = feed_forward_post_norm
+
+    def streamed_weights(self):
+        out = []
+        for part in (self.mixer, self.feed_forward):
+            out += list(getattr(part, "streamed_weights", lambda: [])())
+        return out
+
+    def forward(self, stream, ctx, cache):
+        stream.add_normed(self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache), self.mixer_post_norm)
+        if self.feed_forward is not None:
+            stream.add_normed(self.feed_forward.forward(stream.normed(self.feed_forward_norm)),
+                              self.feed_forward_post_norm)
+
+
+class SandwichNormMixerOnly(SandwichNormResidual):
+    """The same arrangement for a layer without a feed-forward."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm"}
+
+
+class PassEntry:
+    """What a pass of a looped stack of layers adds to the stream right before its first layer:
+    the embedding's output (`add_embedding`: every pass but the first) and row `index` of a
+    tensor [passes, hidden] (`tensor`)."""
+
+    @staticmethod
+    def tensors(spec):
+        return [TensorSpec(spec.params["tensor"], (spec.params["passes"], spec.params["hidden_size"]))]
+
+    def __init__(self, spec, store, runtime):
+        p = spec.params
+        if not 0 <= int(p["index"]) < int(p["passes"]):
+            raise ValueError(f"pass {p['index']} of {p['passes']}")
+        self.needs_embedding = bool(p.get("add_embedding"))
+        self.vector = runtime.vector(store.get(p["tensor"])[int(p["index"])])
+
+    def forward(self, stream, embedded):
+        ops.stream_inject(stream.flush(), embedded if self.needs_embedding else None, self.vector)
+
+
+register_part("block", "sandwich_norm_residual", SandwichNormResidual)
+register_part("block", "sandwich_norm_mixer_only", SandwichNormMixerOnly)
+register_part("injection", "pass_entry", PassEntry)

@@ -22,10 +22,13 @@ class TokenEmbedding:
         self.runtime = runtime
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
         self.table = runtime.matrix(store.get(tensor_name(spec)))
+        # `scale` (optional): the looked-up row is multiplied by it, in float32; a head tied to
+        # the table uses the table itself, without it
+        self.scale = float(spec.params.get("scale", 1.0))
 
     def forward(self, ids):
         x = self.runtime.empty(ids.shape[0], self.hidden, dtype=torch.float32)
-        ops.embed(ids, self.table, x)
+        ops.embed(ids, self.table, x, self.scale)
         return x
 
 

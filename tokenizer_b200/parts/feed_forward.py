@@ -27,14 +27,21 @@ FUSED_ROWS = 8
 FUSED_HIDDEN = 1024
 
 
+def _names(spec):
+    """The three matrices' names behind the prefix: `params["names"]` = (gate, up, down) where the
+    file names them otherwise than `.gate_proj.weight`, `.up_proj.weight`, `.down_proj.weight`."""
+    return tuple(spec.params.get("names") or (".gate_proj.weight", ".up_proj.weight", ".down_proj.weight"))
+
+
 class GatedMLP:
     @staticmethod
     def tensors(spec):
         p, x = spec.params, spec.prefix
+        gate, up, down = _names(spec)
         return [
-            TensorSpec(x + ".gate_proj.weight", (p["intermediate_size"], p["hidden_size"])),
-            TensorSpec(x + ".up_proj.weight", (p["intermediate_size"], p["hidden_size"])),
-            TensorSpec(x + ".down_proj.weight", (p["hidden_size"], p["intermediate_size"])),
+            TensorSpec(x + gate, (p["intermediate_size"], p["hidden_size"])),
+            TensorSpec(x + up, (p["intermediate_size"], p["hidden_size"])),
+            TensorSpec(x + down, (p["hidden_size"], p["intermediate_size"])),
         ]
 
     def __init__(self, spec, store, runtime):
@@ -45,7 +52,8 @@ class GatedMLP:
         self.activation = p["activation"]
         self.runtime = runtime
         self.inner = int(p["intermediate_size"])
-        gate, up = store.get(x + ".gate_proj.weight"), store.get(x + ".up_proj.weight")
+        gate_name, up_name, down_name = _names(spec)
+        gate, up = store.get(x + gate_name), store.get(x + up_name)
         hidden = int(p["hidden_size"])
         # bfloat16 with sizes the gated kernels take: the activation is folded into the
         # product's epilogue and the stacked weight is laid out for that
@@ -55,7 +63,7 @@ class GatedMLP:
             self.gate_up_weight = ops.interleave_gate_up(runtime.matrix(gate), runtime.matrix(up))
         else:
             self.gate_up = Linear(runtime.matrix(torch.cat([gate, up], dim=0)))
-        self.down = Linear(runtime.matrix(store.get(x + ".down_proj.weight")))
+        self.down = Linear(runtime.matrix(store.get(x + down_name)))
 
     def fused_step(self, stream, norm) -> bool:
         """For few rows in bfloat16: residual add, norm, both products and the activation
@@ -148,5 +156,68 @@ class PolyNormMLP(SideProjection):
         return self.down.forward(act)
 
 
+class RoutedMLP:
+    """A feed-forward of `experts` small gated feed-forwards (`<prefix>.e<i>.gate`, `.up`, `.down`,
+    inner size `expert_inner`, no biases), of which every token uses the `top` with the largest
+    router logits z = W_router h (32-bit sums), weighed by the softmax over those logits alone; and,
+    with `shared_inner`, one more of that form (`<prefix>.shared.*`) that every token uses, scaled by
+    sigmoid(W_sg h) (`.shared.sg`, one row).
+
+    How it is computed: as ONE gated feed-forward whose inner lanes are all experts' lanes side by
+    side, the shared expert's behind them.  The gate/up product is one stacked product; every inner
+    lane is then scaled by its expert's share for the token, zero for an expert the token did not
+    choose (`csrc/moe.cu`); the down product over all lanes is the weighted sum of the chosen
+    experts' outputs.  Nothing depends on values read back to the host, so a step can be captured.
+    It costs experts / top times the routed experts' arithmetic: what a model of few experts pays
+    for products of full size instead of a product per expert over gathered rows."""
+
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        hidden, inner = p["hidden_size"], p["expert_inner"]
+        out = []
+        for e in range(p["experts"]):
+            out += [TensorSpec(f"{x}.e{e}.gate", (inner, hidden)), TensorSpec(f"{x}.e{e}.up", (inner, hidden)),
+                    TensorSpec(f"{x}.e{e}.down", (hidden, inner))]
+        out.append(TensorSpec(x + ".router", (p["experts"], hidden)))
+        if p.get("shared_inner"):
+            s = p["shared_inner"]
+            out += [TensorSpec(x + ".shared.gate", (s, hidden)), TensorSpec(x + ".shared.up", (s, hidden)),
+                    TensorSpec(x + ".shared.down", (hidden, s)), TensorSpec(x + ".shared.sg", (1, hidden))]
+        return out
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        self.runtime = runtime
+        self.experts, self.top, self.ff = int(p["experts"]), int(p["top"]), int(p["expert_inner"])
+        self.shared = int(p.get("shared_inner") or 0)
+        self.activation = p.get("activation", "silu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ConfigError(f"routed feed-forward knows the activations {', '.join(ops.ACTIVATIONS)}; "
+                              f"found {self.activation}")
+        if not 1 <= self.top <= self.experts or self.experts > 1024:
+            raise ConfigError(f"a token uses 1 .. experts of at most 1024 experts; found top {self.top} of {self.experts}")
+        names = [f"{x}.e{e}" for e in range(self.experts)] + ([x + ".shared"] if self.shared else [])
+        self.inner = self.experts * self.ff + self.shared
+        gates = torch.cat([store.get(n + ".gate") for n in names], dim=0)
+        ups = torch.cat([store.get(n + ".up") for n in names], dim=0)
+        self.gate_up = Linear(runtime.matrix(torch.cat([gates, ups], dim=0)))
+        self.down = Linear(runtime.matrix(torch.cat([store.get(n + ".down") for n in names], dim=1)))
+        rows = [store.get(x + ".router")] + ([store.get(x + ".shared.sg")] if self.shared else [])
+        self.router = runtime.vector(torch.cat(rows, dim=0))       # float32: the logits are 32-bit
+
+    def streamed_weights(self):
+        return [self.gate_up.weight, self.down.weight]
+
+    def forward(self, h):
+        n = h.shape[0]
+        share = torch.empty((n, self.experts + (1 if self.shared else 0)), dtype=torch.float32, device=h.device)
+        ops.moe_route(h, self.router, self.experts, self.top, bool(self.shared), share)
+        act = self.runtime.empty(n, self.inner)
+        ops.moe_gate(self.gate_up.forward(h), share, act, self.experts, self.ff, bool(self.shared), self.activation)
+        return self.down.forward(act, partials_ok=True)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "routed_mlp", RoutedMLP)
 register_part("feed_forward", "poly_norm_mlp", PolyNormMLP)

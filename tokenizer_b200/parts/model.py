@@ -34,9 +34,17 @@ def declared_tensors(spec: ModelSpec) -> List[TensorSpec]:
     for layer in spec.layers:
         for category, part in layer_parts(layer):
             out += part_class(category, part.kind).tensors(part)
+    for call in spec.order:
+        if call.before is not None:
+            out += part_class("injection", call.before.kind).tensors(call.before)
     out += part_class("norm", spec.final_norm.kind).tensors(spec.final_norm)
     out += part_class("head", spec.head.kind).tensors(spec.head)
-    return out
+    seen, once = set(), []
+    for tensor in out:                 # several calls of the order may name one tensor
+        if tensor.name not in seen:
+            seen.add(tensor.name)
+            once.append(tensor)
+    return once
 
 
 # TOKB200_L2_PREFETCH=1: while a step of few rows runs a layer, a second stream brings the next
@@ -85,6 +93,10 @@ class DecoderModel:
         tied = self.embedding.table if spec.head.params.get("tied_to") else None
         self.head = head_cls(spec.head, store, runtime, tied_table=tied)
         self.order = spec.order
+        # what a call of the order does to the stream before its layer runs (None: nothing)
+        self.before = [None if call.before is None else build_part("injection", call.before, store, runtime)
+                       for call in spec.order]
+        self._keep_embedding = any(getattr(part, "needs_embedding", False) for part in self.before)
         self._side = None
         self.scratch = ops.ScratchSpace()      # what this model's kernels use beyond inputs and outputs
 
@@ -148,8 +160,12 @@ class DecoderModel:
 
     def _forward(self, ctx, bindings, want_rows):
         stream = ResidualStream(self.embedding.forward(ctx.ids))
+        # norms add in place: a part that adds the embedding's output again later gets a copy
+        embedded = stream.x.clone() if self._keep_embedding else None
         ahead = self._prefetcher(ctx)
         for at, (call, binding) in enumerate(zip(self.order, bindings)):
+            if self.before[at] is not None:
+                self.before[at].forward(stream, embedded)
             if ahead is not None and at + 1 < len(self.order):
                 ahead.fetch(self.blocks[self.order[at + 1].layer].streamed_weights())
             ctx.next_block = self.blocks[self.order[at + 1].layer] if at + 1 < len(self.order) else None

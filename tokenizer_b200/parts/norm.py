@@ -1,5 +1,5 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * gain, statistics in float32
-(reference: qwen-infer/src/model.rs:594-599, 616, 749)."""
+(reference: qwen-infer/src/model.rs:594-599, 616, 749); and the layer norm with gain and bias."""
 from __future__ import annotations
 
 import torch
@@ -48,4 +48,51 @@ class RMSNorm:
         return out
 
 
+class LayerNorm:
+    """(x - mean) / sqrt(var + eps) * gain + bias, var the mean of the squared deviations; the
+    bias is the tensor of the gain's name with `.b` added.  Statistics in float32, two passes.
+    As the norm on a sublayer's OUTPUT it offers `add_to`: x += norm(sum of the output's scaled
+    terms), and, where the next norm is of this kind too, that norm of the new x in the same
+    kernel (`csrc/layer_norm.cu`)."""
+
+    @staticmethod
+    def tensors(spec):
+        name = tensor_name(spec)
+        return [TensorSpec(name, (spec.params["size"],), "one_plus_normal"),
+                TensorSpec(name + ".b", (spec.params["size"],), "normal")]
+
+    def __init__(self, spec, store, runtime):
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.runtime = runtime
+        name = tensor_name(spec)
+        self.gain = runtime.vector(store.get(name))
+        self.bias = runtime.vector(store.get(name + ".b"))
+
+    def affine(self):
+        """(gain, bias, eps) for a kernel that computes this norm behind its own work."""
+        return self.gain, self.bias, self.eps
+
+    def add_to(self, x, terms, then=None):
+        """x += this norm of the summed terms, in place; with `then` (the norm in front of the next
+        sublayer), returns that norm of the new x."""
+        following = getattr(then, "affine", None)
+        if then is None or following is None:
+            ops.post_norm_add(x, terms, self.gain, self.bias, self.eps)
+            return None if then is None else then.forward(x)
+        gain, bias, eps = following()
+        out = self.runtime.empty(x.shape[0], self.size)
+        ops.post_norm_add(x, terms, self.gain, self.bias, self.eps, gain, bias, eps, out)
+        return out
+
+    def forward(self, x, delta=None, rows=None):
+        if delta is not None:
+            ops.residual_add(x, delta)
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = self.runtime.empty(n, self.size)
+        ops.layer_norm(x, self.gain, self.bias, self.eps, out, rows=rows)
+        return out
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm", LayerNorm)

@@ -1,4 +1,6 @@
-"""minGRU: a gated recurrence whose gates read only the current token.
+"""Recurrent mixers: minGRU and the gated delta rule (`GatedDeltaNet`, below).
+
+minGRU: a gated recurrence whose gates read only the current token.
 
 For a token's input h: z = sigmoid(Wz h + bz), u = Wx h + bx, candidate = u + 1/2 where u >= 0 and
 sigmoid(u) below, state S_t = (1 - z) S_(t-1) + z candidate element by element, output
@@ -11,6 +13,7 @@ from __future__ import annotations
 
 import torch
 
+from ..config.spec import ConfigError
 from ..kernels import ops
 from ..weights.store import TensorSpec
 from .base import CacheNeed, StateNeed, register_part
@@ -93,4 +96,105 @@ class MinGRU(SideProjection):
         return self.out.forward(y, partials_ok=True)
 
 
+def stacked_rows(weights, multiple: int = 8):
+    """The matrices one under the other, with zero rows behind them up to a whole `multiple` of rows
+    (rows of the float32 product then start on 32 bytes)."""
+    rows = sum(w.shape[0] for w in weights)
+    spare = -rows % multiple
+    if spare:
+        weights = list(weights) + [torch.zeros((spare, weights[0].shape[1]), dtype=weights[0].dtype)]
+    return torch.cat(weights, dim=0)
+
+
+class GatedDeltaNet:
+    """The gated delta rule: per head a matrix state S (dim x vdim, float32) that every token
+    decays, corrects along its key and reads along its query:
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+    From the mixer's input h: q = Wq h and k = Wk h (kv_heads x dim; value head i uses q/k head
+    i // (heads / kv_heads)), v = Wv h (heads x vdim); each of the three passes a short causal
+    convolution over time, channel by channel (`<tensor>.conv` [channels, taps], the last tap on the
+    current token, zeros before a sequence's start), and silu; q and k become unit vectors per head
+    (x / sqrt(sum x^2 + 1e-6)), q also times dim^(-1/2); beta = sigmoid(Wb h) and the decay
+    g = exp(-exp(A_log) softplus(Wa h + dt_bias)), one a head; every head's o is divided by its root
+    mean square over vdim, scaled by the gain `norm` (vdim lanes, shared by the heads) and by
+    silu(Wg h); then Wo.  Everything behind the six input products (one stacked product, written
+    in float32) is 32-bit (`csrc/delta_rule.cu`).
+
+    Per request it keeps, in one state slot: the heads' matrices and the convolution's last
+    taps - 1 inputs.  `input_stack` / `forward_projected`: a mixer that runs beside another one on
+    the same input may have its input products computed in one product with the other's."""
+
+    graph_safe = True    # launches depend on device-side metadata alone
+
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        hidden, heads, groups, dim, vdim, taps = (p["hidden_size"], p["heads"], p["kv_heads"], p["dim"], p["vdim"],
+                                                  p["conv"])
+        return [TensorSpec(x + ".q", (groups * dim, hidden)), TensorSpec(x + ".q.conv", (groups * dim, taps), "normal", 0.5),
+                TensorSpec(x + ".k", (groups * dim, hidden)), TensorSpec(x + ".k.conv", (groups * dim, taps), "normal", 0.5),
+                TensorSpec(x + ".v", (heads * vdim, hidden)), TensorSpec(x + ".v.conv", (heads * vdim, taps), "normal", 0.5),
+                TensorSpec(x + ".b", (heads, hidden)), TensorSpec(x + ".A_log", (heads,), "normal", 0.5),
+                TensorSpec(x + ".norm", (vdim,), "one_plus_normal"), TensorSpec(x + ".a", (heads, hidden)),
+                TensorSpec(x + ".dt_bias", (heads,), "normal", 0.5), TensorSpec(x + ".g", (heads * vdim, hidden)),
+                TensorSpec(x + ".o", (hidden, heads * vdim))]
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        self.runtime = runtime
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.groups = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim, self.taps = int(p["dim"]), int(p["vdim"]), int(p["conv"])
+        self.eps = float(p["eps"])
+        if self.groups <= 0 or self.heads % self.groups:
+            raise ConfigError(f"{self.heads} value heads do not divide into {self.groups} query/key heads")
+        self.dim_padded = ops.gdn_padded_dim(self.dim)
+        if not self.dim_padded or not 1 <= self.taps <= 16:
+            raise ConfigError(f"the delta rule takes heads of up to 1024 lanes and convolutions of up to 16 taps; "
+                              f"found {self.dim} and {self.taps}")
+        self.channels = 2 * self.groups * self.dim + self.heads * self.vdim
+        self._stack = [store.get(x + "." + n) for n in ("q", "k", "v", "b", "a", "g")]
+        self.conv_w = runtime.vector(torch.cat([store.get(x + f".{n}.conv").to(torch.float32) for n in "qkv"], dim=0))
+        self.a_log = runtime.vector(store.get(x + ".A_log"))
+        self.dt_bias = runtime.vector(store.get(x + ".dt_bias"))
+        self.gain = runtime.vector(store.get(x + ".norm"))
+        self.out = Linear(runtime.matrix(store.get(x + ".o")))
+        self.inputs = None                      # built at first use: a mixer beside this one may carry the product
+        # a slot: [heads, vdim, dim_padded] and behind it [taps - 1, channels], in whole 4s of floats
+        self.conv_off = self.heads * self.vdim * self.dim_padded
+        self.state_floats = -(-(self.conv_off + (self.taps - 1) * self.channels) // 4) * 4
+
+    def input_stack(self):
+        """(the six input matrices one under the other, as stored; their bias: none)."""
+        return torch.cat(self._stack, dim=0), None
+
+    def cache_need(self):
+        return CacheNeed(state=StateNeed((self.state_floats,)))
+
+    def streamed_weights(self):
+        return [self.out.weight] if self.inputs is None else [self.inputs.weight, self.out.weight]
+
+    def forward_projected(self, proj, at, ctx, cache, out_scale: float = 1.0):
+        """From the stacked product `proj` (float32 or the compute type), this mixer's columns
+        starting at `at`; the output is scaled by `out_scale` (in float32, before it is rounded for
+        the output projection)."""
+        n, c, h = ctx.n_tokens, self.channels, self.heads
+        qkv = torch.empty((n, c), dtype=torch.float32, device=proj.device)
+        bg = torch.empty((n, 2 * h), dtype=torch.float32, device=proj.device)
+        ops.gdn_prepare(proj, at, at + c, at + c + h, self.groups, h, self.dim, self.vdim, self.taps, self.conv_w,
+                        self.a_log, self.dt_bias, cache.state, self.conv_off, ctx.row_req, ctx.q_start,
+                        ctx.state_slot, qkv, bg)
+        o = torch.empty((n, h * self.vdim), dtype=torch.float32, device=proj.device)
+        ops.gdn_scan(qkv, bg, self.groups, h, self.dim, self.vdim, cache.state, ctx.q_start, ctx.state_slot, o)
+        y = self.runtime.empty(n, h * self.vdim)
+        ops.gdn_out_norm(o, proj, at + c + 2 * h, self.gain, out_scale, self.eps, y, h, self.vdim, ctx.row_req)
+        return self.out.forward(y, partials_ok=True)
+
+    def forward(self, h, ctx, cache):
+        if self.inputs is None:
+            self.inputs = Linear(self.runtime.matrix(stacked_rows([self.input_stack()[0]])))
+        return self.forward_projected(self.inputs.forward(h, out_dtype=torch.float32), 0, ctx, cache)
+
+
 register_part("mixer", "min_gru", MinGRU)
+register_part("mixer", "gated_delta_net", GatedDeltaNet)
