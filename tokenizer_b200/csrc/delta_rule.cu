@@ -131,7 +131,7 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
   pdl_launch();
   if (first >= last) return;
   // a buffer: k [run][dim_p], q [run][dim_p], v [run][cols], beta [run], decay [run]
-  const int per = run * (2 * dim_p + cols + 2);
+  const int per = (run * (2 * dim_p + cols + 2) + 3) / 4 * 4;     // whole 16 bytes: the rows are read as float4
   for (int i = threadIdx.x; i < 2 * per; i += blockDim.x) gdn_stage[i] = 0.f;   // the padded lanes stay zero
   __syncthreads();
   const int g = h / (heads / groups);
@@ -306,10 +306,10 @@ TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, 
   const int cols = GDN_THREADS / P;
   const int dim_p = P * dpl;
   // tokens a run: what two buffers of 48 KB together hold, at most 16
-  int run = (48 * 1024 / 2 / (int)sizeof(float)) / (2 * dim_p + cols + 2);
+  int run = (48 * 1024 / 2 / (int)sizeof(float) - 4) / (2 * dim_p + cols + 2);
   run = run > 16 ? 16 : run;
   if (run < 1) return TOKB200_BAD_SIZE;
-  const size_t smem = (size_t)2 * run * (2 * dim_p + cols + 2) * sizeof(float);
+  const size_t smem = (size_t)2 * ((run * (2 * dim_p + cols + 2) + 3) / 4 * 4) * sizeof(float);
   dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
   if (dpl == 8)
     return launch_dependent(gdn_scan_kernel<8>, grid, dim3(GDN_THREADS), smem, stream, qkv, bg, channels, groups,
