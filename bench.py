@@ -3,7 +3,7 @@
 weights on one B200.  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 0.5b|1.5b-mixed|7b|pufuzen]
+                    [--config 0.5b|1.5b-mixed|7b|pufuzen|katopel]
 
 A "step" is one decode step of the whole batch.  `value` is decoded tokens a
 second timed on the device over K steps that never return to the host
@@ -196,11 +196,11 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen"],
+    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen", "katopel"],
                         help="0.5b: the headline line; 7b: the same at Qwen2.5-7B sizes with 8,192-token "
                              "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes; "
                              "pufuzen: prefill and decoding of the Pufuzen design at two widths beside Qwen2 at "
-                             "equal width, depth and parameters, and its kernels alone")
+                             "equal width, depth and parameters, and its kernels alone; katopel: the same for the Katopel design")
     parser.add_argument("--context", type=int, default=8192, help="--config 7b: tokens held before decoding")
     parser.add_argument("--layer-phases", action="store_true",
                         help="print where the time of the whole-layer kernel (TOKB200_LAYER=fused) goes, phase by "
@@ -214,6 +214,8 @@ def main():
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--only-decode", action="store_true",
                         help="time the decode steps only and print a short line (for profiling)")
+    parser.add_argument("--only-kernels", action="store_true",
+                        help="--config katopel: the kernels alone, without the models")
     parser.add_argument("--only-prefill", action="store_true",
                         help="time the 2,048-token prefill only and print a short line (for profiling)")
     args = parser.parse_args()
@@ -237,6 +239,8 @@ def main():
         return run_mixed(args)
     if args.config == "pufuzen":
         return run_pufuzen(args)
+    if args.config == "katopel":
+        return run_katopel(args)
     args.steps = max(1, min(args.steps, NEW_TOKENS - args.warmup - 1))
 
     import torch
@@ -661,6 +665,67 @@ def run_7b(args):
     return 0
 
 
+# ---- a design's prefill and decoding, timed on the device ----
+def device_timed(fn, reps=1):
+    import torch
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        out = fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / reps, out
+
+def measure_design(config, vocab, args, gen, context, steps):
+    """Prefill of PREFILL_TOKENS tokens (one step, median of five) and decoding at batch 1 and `--batch` with
+    `context`-token contexts, `steps` steps on the device, of a model of `config` with random weights."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    from tokenizer_b200.kernels import ops
+    from tokenizer_b200.parts.model import declared_tensors
+    timed = device_timed
+    model = tb.random_model(config, seed=3, dtype="bfloat16", device="cuda:0")
+    params = sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
+    batches = sorted({1, args.batch})
+    engine = tb.engine_for(model, max(batches) * (context + steps + args.warmup + 4 * PAGE), PAGE,
+                           max_requests=max(batches), share_prefixes=False)
+    ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+    prefill = []
+    for rep in range(3 + 5):
+        cache = engine.cache.open(("prefill", rep))
+        engine.cache.reserve(cache, PREFILL_TOKENS)
+        entry = StepEntry(cache, ids(PREFILL_TOKENS), [PREFILL_TOKENS - 1])
+        ms, _ = timed(lambda: engine.step([entry]))
+        if rep >= 3:
+            prefill.append(ms)
+        engine.cache.close(cache)
+    out = {"parameters_m": round(params / 1e6, 1), "prefill_ms": sorted(prefill)[len(prefill) // 2]}
+    out["prefill_tok_s"] = PREFILL_TOKENS / (out["prefill_ms"] / 1e3)
+    for batch in batches:
+        caches = [engine.cache.open(("decode", batch, i)) for i in range(batch)]
+        nexts = []
+        for lo in range(0, batch, 4):
+            group = caches[lo:lo + 4]
+            for c in group:
+                engine.cache.reserve(c, context)
+            logits = engine.step([StepEntry(c, ids(context), [context - 1]) for c in group])
+            nexts += engine.sampler.greedy(logits).tolist()
+        drawn = engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, nexts)], args.warmup)
+        launches = ops.counter.launches
+        ms, _ = timed(lambda: engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, drawn[-1])], steps))
+        out[f"decode_b{batch}_ms"] = ms / steps
+        out[f"decode_b{batch}_tok_s"] = batch * steps / (ms / 1e3)
+        out[f"decode_b{batch}_launches_a_step"] = (ops.counter.launches - launches) // steps
+        for c in caches:
+            engine.cache.close(c)
+    engine.check()
+    del engine, model
+    torch.cuda.empty_cache()
+    return out
+
+
 # ---- the Pufuzen design beside the Qwen2 decoder at equal width, depth and parameter count ----
 PUFUZEN_SIZES = {
     # width, heads, dim / vdim of a head, query and key/value latents, positional lanes, recurrence width,
@@ -707,55 +772,10 @@ def run_pufuzen(args):
     gen = torch.Generator().manual_seed(99)
     context, steps = 2048, max(8, min(args.steps, 64))
 
-    def timed(fn, reps=1):
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(reps):
-            out = fn()
-        stop.record()
-        torch.cuda.synchronize()
-        return start.elapsed_time(stop) / reps, out
+    timed = device_timed
 
     def measure(config, vocab):
-        model = tb.random_model(config, seed=3, dtype="bfloat16", device="cuda:0")
-        params = sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
-        batches = sorted({1, args.batch})
-        engine = tb.engine_for(model, max(batches) * (context + steps + args.warmup + 4 * PAGE), PAGE,
-                               max_requests=max(batches), share_prefixes=False)
-        ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
-        prefill = []
-        for rep in range(3 + 5):
-            cache = engine.cache.open(("prefill", rep))
-            engine.cache.reserve(cache, PREFILL_TOKENS)
-            entry = StepEntry(cache, ids(PREFILL_TOKENS), [PREFILL_TOKENS - 1])
-            ms, _ = timed(lambda: engine.step([entry]))
-            if rep >= 3:
-                prefill.append(ms)
-            engine.cache.close(cache)
-        out = {"parameters_m": round(params / 1e6, 1), "prefill_ms": sorted(prefill)[len(prefill) // 2]}
-        out["prefill_tok_s"] = PREFILL_TOKENS / (out["prefill_ms"] / 1e3)
-        for batch in batches:
-            caches = [engine.cache.open(("decode", batch, i)) for i in range(batch)]
-            nexts = []
-            for lo in range(0, batch, 4):
-                group = caches[lo:lo + 4]
-                for c in group:
-                    engine.cache.reserve(c, context)
-                logits = engine.step([StepEntry(c, ids(context), [context - 1]) for c in group])
-                nexts += engine.sampler.greedy(logits).tolist()
-            drawn = engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, nexts)], args.warmup)
-            launches = ops.counter.launches
-            ms, _ = timed(lambda: engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, drawn[-1])], steps))
-            out[f"decode_b{batch}_ms"] = ms / steps
-            out[f"decode_b{batch}_tok_s"] = batch * steps / (ms / 1e3)
-            out[f"decode_b{batch}_launches_a_step"] = (ops.counter.launches - launches) // steps
-            for c in caches:
-                engine.cache.close(c)
-        engine.check()
-        del engine, model
-        torch.cuda.empty_cache()
-        return out
+        return measure_design(config, vocab, args, gen, context, steps)
 
     models = {}
     for name, z in PUFUZEN_SIZES.items():
@@ -860,6 +880,199 @@ def run_pufuzen(args):
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
         "data": "synthetic: random weights drawn on the device, uniform random token ids",
         "config": {"sizes": PUFUZEN_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
+                   "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
+        "models": models, "kernels": kernels}))
+    return 0
+
+
+# ---- the Katopel design beside the Qwen2 decoder at equal width, depth and parameter count ----
+KATOPEL_SIZES = {
+    # width; the attention beside the delta rule (heads over kv heads of dim / vdim lanes, chunks of `chunk`
+    # positions, `rot` rotated lanes); the delta rule (heads over kv heads, dim x vdim matrices, taps); dense and
+    # expert feed-forward widths (experts, of which a token uses `top`, and a shared one)
+    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, chunk=1024, rot=32, d_heads=8, d_kv=4, d_dim=128,
+               d_vdim=128, taps=4, ff=2816, experts=8, top=2, expert_ff=704, shared_ff=1408, vocab=32000, layers=8,
+               qwen_head_dim=64),
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, rot=64, d_heads=16, d_kv=8, d_dim=128,
+               d_vdim=128, taps=4, ff=5632, experts=8, top=2, expert_ff=1408, shared_ff=2816, vocab=32000, layers=8,
+               qwen_head_dim=128),
+}
+
+
+def katopel_config(z):
+    """Layers in the pattern delta rule + dense, two mixers side by side + experts, two mixers side by side +
+    dense, delta rule + experts; no loop, so that every layer has weights of its own as in the model beside it."""
+    import tokenizer_b200 as tb
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    delta = {"heads": z["d_heads"], "kv_heads": z["d_kv"], "dim": z["d_dim"], "vdim": z["d_vdim"], "conv": z["taps"]}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["chunk"]}, "rot": {"base": 1000000.0, "dims": z["rot"]}}
+    side = {"left": left, "right": delta, "left_scale": 0.6, "right_scale": 1.1}
+    pattern = [{"type": "delta", "mixer": delta, "mlp": dense}, {"type": "parallel", "mixer": side, "mlp": moe},
+               {"type": "parallel", "mixer": side, "mlp": dense}, {"type": "delta", "mixer": delta, "mlp": moe}]
+    return tb.config.KatopelConfig.from_dict({
+        "architecture": "Katopel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+        "embedding": {"scale": 2.0}, "layers": [pattern[i % 4] for i in range(z["layers"])]})
+
+
+def run_katopel(args):
+    """Prefill (one step of 2,048 tokens) and decoding (batch 1 and `--batch`, 2,048-token contexts) of the
+    Katopel design at two widths, beside the Qwen2 decoder of the same width, depth and heads with the
+    feed-forward width that gives it the same parameters; then the design's own kernels alone beside the like
+    kernels of the paths that were there before, each on inputs larger than L2, against the measured copy peak."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.kernels import ops
+    from tokenizer_b200.parts.model import declared_tensors
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(99)
+    context, steps = 2048, max(8, min(args.steps, 64))
+    timed = device_timed
+    count = lambda config: sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
+
+    def qwen_config(z, inner):
+        return tb.Qwen2Config.from_dict(dict(
+            architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=z["layers"],
+            hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+            head_dim=z["qwen_head_dim"], intermediate_size=inner, vocab_size=z["vocab"], rope_theta=1000000.0,
+            rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768, use_sliding_window=False,
+            sliding_window=32768, max_window_layers=z["layers"]))
+
+    models = {}
+    for name, z in KATOPEL_SIZES.items():
+        if args.only_kernels:
+            break
+        config = katopel_config(z)
+        models[name] = {"katopel": measure_design(config, z["vocab"], args, gen, context, steps)}
+        # the gated feed-forward width (whole 128s) that brings Qwen2 to the same parameters
+        base, step = count(qwen_config(z, 128)), count(qwen_config(z, 256)) - count(qwen_config(z, 128))
+        inner = max(1, round((count(config) - base) / step) + 1) * 128
+        models[name]["qwen2"] = dict(measure_design(qwen_config(z, inner), z["vocab"], args, gen, context, steps),
+                                     intermediate_size=inner)
+
+    # ---- kernels alone: inputs larger than L2, a 256 MB write between the timed launches ----
+    dev = "cuda:0"
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def kernel_time(fn, reps=7):
+        times = []
+        for _ in range(3 + reps):
+            flush.zero_()
+            ms, _ = timed(fn)
+            times.append(ms)
+        return sorted(times[3:])[reps // 2]
+
+    kernels = {}
+
+    def record(name, ms, nbytes, like, flops=None):
+        kernels[name] = {"us": round(ms * 1e3, 1), "gb_s": round(nbytes / (ms / 1e3) / 1e9), "like": like,
+                         "of_measured_copy_peak": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 2)}
+        if flops is not None:
+            kernels[name]["fp32_tflops"] = round(flops / (ms / 1e3) / 1e12, 1)
+
+    ints = lambda values: torch.tensor(list(values), dtype=torch.int32, device=dev)
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, device=dev, dtype=torch.float32).to(dtype)
+    T, H, I = 8192, 2048, 5632
+    heads, groups, dim, vdim, taps = 16, 8, 128, 128, 4
+    channels = 2 * groups * dim + heads * vdim
+    padded = ops.gdn_padded_dim(dim)
+    conv_off = heads * vdim * padded
+    slot_floats = -(-(conv_off + (taps - 1) * channels) // 4) * 4
+    proj = rnd(T, channels + 2 * heads + heads * vdim)
+    conv, a_log, dt_bias = rnd(channels, taps), rnd(heads), rnd(heads)
+    qkv, bg = torch.empty(T, channels, device=dev), torch.empty(T, 2 * heads, device=dev)
+    o = torch.empty(T, heads * vdim, device=dev)
+    y16 = torch.empty(T, heads * vdim, dtype=torch.bfloat16, device=dev)
+    gain_v = torch.ones(vdim, device=dev)
+    for requests in (1, 4):
+        state = torch.zeros(requests, slot_floats, device=dev)
+        spans, slots = ints(T * r // requests for r in range(requests + 1)), ints(range(requests))
+        row_req = ints(r for r in range(requests) for _ in range(T // requests))
+        record(f"gdn_prepare, {T} tokens of {requests} request(s), {channels} channels of {taps} taps",
+               kernel_time(lambda: ops.gdn_prepare(proj, 0, channels, channels + heads, groups, heads, dim, vdim, taps, conv,
+                                                   a_log, dt_bias, state, conv_off, row_req, spans, slots, qkv, bg)),
+               T * (channels + 2 * heads) * 8, "rope_store")
+        record(f"gdn_scan, {T} tokens of {requests} request(s), {heads} heads of {dim} x {vdim}",
+               kernel_time(lambda: ops.gdn_scan(qkv, bg, groups, heads, dim, vdim, state, spans, slots, o)),
+               T * (channels + 2 * heads + heads * vdim) * 4, "min_gru_scan", flops=T * heads * dim * vdim * 8)
+    record(f"gdn_out_norm, {T} tokens x {heads} heads of {vdim}",
+           kernel_time(lambda: ops.gdn_out_norm(o, proj, channels + 2 * heads, gain_v, 1.0, 1e-6, y16, heads, vdim, row_req)),
+           T * heads * vdim * (4 + 4 + 2), "silu_gate")
+    # decoding: 64 requests of one token each; the matrices are read and written once a token
+    rows = 64
+    state = torch.zeros(rows, slot_floats, device=dev)
+    spans, slots = ints(range(rows + 1)), ints(range(rows))
+    record(f"gdn_scan, {rows} requests of one token, {heads} heads of {dim} x {vdim}",
+           kernel_time(lambda: ops.gdn_scan(qkv[:rows], bg[:rows], groups, heads, dim, vdim, state, spans, slots, o[:rows])),
+           rows * conv_off * 8, "decode attention")
+    x, y = rnd(T, H), rnd(T, H, dtype=torch.bfloat16)
+    g1, b1 = torch.ones(H, device=dev), torch.zeros(H, device=dev)
+    h16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    record(f"post_norm_add with the next norm, {T} x {H}",
+           kernel_time(lambda: ops.post_norm_add(x, [(y, 1.0)], g1, b1, 1e-6, g1, b1, 1e-6, h16)), T * H * (2 + 4 + 4 + 2),
+           "rms_norm")
+    two = rnd(2, T, H)
+    record(f"post_norm_add of two scaled terms (float32 partial sums and bfloat16) with the next norm, {T} x {H}",
+           kernel_time(lambda: ops.post_norm_add(x, [(two, 0.6), (y, 1.1)], g1, b1, 1e-6, g1, b1, 1e-6, h16)),
+           T * H * (8 + 2 + 4 + 4 + 2), "rms_norm")
+    nh, nkv, d = 16, 4, 128
+    wide = rnd(T, (nh + 2 * nkv) * d + 64)
+    bias = torch.zeros((nh + 2 * nkv) * d, device=dev)
+    freq = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    req = torch.zeros(T, dtype=torch.int32, device=dev)
+    q_out = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+    k_pool = torch.zeros(T + 64, nkv, d, dtype=torch.bfloat16, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    record(f"qkv_rotate_store, {T} tokens, {nh} heads over {nkv} of {d} lanes, 64 rotated",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 64, bias, freq, 64, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d)),
+           T * (nh + 2 * nkv) * d * (4 + 2), "rope_store")
+    experts, ff, shared_ff = 8, 512, 1536
+    gu = rnd(T, 2 * I, dtype=torch.bfloat16)
+    share = torch.rand(T, experts + 1, device=dev)
+    act = torch.empty(T, I, dtype=torch.bfloat16, device=dev)
+    record(f"moe_gate, {T} x {I} lanes of {experts} experts and a shared one",
+           kernel_time(lambda: ops.moe_gate(gu, share, act, experts, ff, True)), T * I * 6, "silu_gate")
+    h_in = rnd(T, H, dtype=torch.bfloat16)
+    router = rnd(experts + 1, H)
+    record(f"moe_route, {T} tokens, {experts} experts of which 2, width {H}",
+           kernel_time(lambda: ops.moe_route(h_in, router, experts, 2, True, share)), T * H * 2, "rms_norm")
+    # the like kernels of the paths that were there before
+    record(f"silu_gate, {T} x {I}", kernel_time(lambda: ops.silu_gate(gu, act)), T * I * 6, None)
+    gain = torch.ones(H, device=dev)
+    record(f"rms_norm with pending add, {T} x {H}", kernel_time(lambda: ops.rms_norm(x, gain, 1e-6, h16, delta=y)),
+           T * H * (4 + 4 + 2 + 2), None)
+    qkv16 = rnd(T, (nh + 2 * nkv) * d, dtype=torch.bfloat16)
+    cos, sin = ops.rope_table(torch.tensor([1e6 ** (-2.0 * i / d) for i in range(d // 2)], device=dev), T)
+    record(f"rope_store, {T} tokens", kernel_time(lambda: ops.rope_store(
+        qkv16, None, pos, pos, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, d)), T * (nh + 2 * nkv) * d * 2 * 2, None)
+    W = 4096
+    gru = rnd(T, 3 * W)
+    gru_state = torch.zeros(4, W, device=dev)
+    out16 = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+    record(f"min_gru_scan, {T} tokens of one request, width {W}",
+           kernel_time(lambda: ops.min_gru_scan(gru, 0, W, 2 * W, W, gru_state, ints([0, T]), ints([0]), T, out16)),
+           T * W * (3 * 4 + 2), None)
+    keys = 8192
+    table = torch.arange(rows * keys // PAGE, dtype=torch.int32, device=dev).view(rows, keys // PAGE)
+    last = torch.full((rows,), keys - 1, dtype=torch.int32, device=dev)
+    kq, vq = rnd(rows * keys, 2, 128, dtype=torch.bfloat16), rnd(rows * keys, 2, 128, dtype=torch.bfloat16)
+    ql = rnd(rows, 16 * 128, dtype=torch.bfloat16)
+    ol = torch.empty_like(ql)
+    record("decode attention, 64 rows x 8,192 keys, 16 heads over 2 of 128 lanes",
+           kernel_time(lambda: ops.decode_attention(ql, kq, vq, ol, table, ints(range(rows)), last, 16, 2, 128, PAGE, None, 0.09)),
+           rows * keys * 2 * 2 * 128 * 2, None)
+    ops.raise_if_error()
+    print(json.dumps({
+        "metric": "prefill and decode tok/s of the Katopel design beside Qwen2 at equal width, depth and parameters",
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
+        "data": "synthetic: random weights drawn on the device, uniform random token ids",
+        "config": {"sizes": KATOPEL_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
                    "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
                    "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
         "models": models, "kernels": kernels}))

@@ -16,7 +16,8 @@
 //   gdn_conv_state   the kept inputs move on (a thread a request and channel, after gdn_prepare)
 //   gdn_scan         the recurrence: the columns of S are independent, so thread (column j, part p)
 //                    keeps DPL rows of column j in registers; the P parts of a column add their
-//                    shares of S^T k and S^T q by shuffles.  Tokens are staged through shared memory
+//                    shares of S^T k and S^T q (both of the matrix before the token's write: the
+//                    read-out after it is g S^T q + (k . q) u) in one round of shuffles.  Tokens are staged through shared memory
 //                    in runs, the next run's copies (cp.async) in flight behind the current one
 //   gdn_out_norm     a warp a (token, head): o / rms(o) * gain * scale * silu(gate)
 #include "common.cuh"
@@ -195,18 +196,27 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
         qq[e] = b.x; qq[e + 1] = b.y; qq[e + 2] = b.z; qq[e + 3] = b.w;
       }
       const float vj = v_s[tok * cols + col], beta = b_s[tok], decay = g_s[tok];
-      float dot = 0.f;
+      // both read-outs from the matrix as it stands: S'^T q = g S^T q + (k . q) u, so that one round of
+      // shuffles serves the token (the chain from token to token is the sums, the round, u, the update)
+      float dk[2] = {0.f, 0.f}, dq[2] = {0.f, 0.f}, kq = 0.f;
 #pragma unroll
-      for (int e = 0; e < DPL; ++e) dot = fmaf(S[e], kk[e], dot);
-      for (int o = P >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = beta * (vj - decay * dot);
-      float out = 0.f;
-#pragma unroll
-      for (int e = 0; e < DPL; ++e) {
-        S[e] = fmaf(kk[e], u, decay * S[e]);
-        out = fmaf(S[e], qq[e], out);
+      for (int e = 0; e < DPL; e += 2) {
+        dk[0] = fmaf(S[e], kk[e], dk[0]);
+        dk[1] = fmaf(S[e + 1], kk[e + 1], dk[1]);
+        dq[0] = fmaf(S[e], qq[e], dq[0]);
+        dq[1] = fmaf(S[e + 1], qq[e + 1], dq[1]);
+        kq = fmaf(kk[e], qq[e], fmaf(kk[e + 1], qq[e + 1], kq));
       }
-      for (int o = P >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      float dot = dk[0] + dk[1], read = dq[0] + dq[1];
+      for (int o = P >> 1; o > 0; o >>= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        read += __shfl_xor_sync(0xffffffffu, read, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
+      const float u = beta * (vj - decay * dot);
+      const float out = fmaf(kq, u, decay * read);
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) S[e] = fmaf(kk[e], u, decay * S[e]);
       if (live && part == 0) o_out[(size_t)(t0 + tok) * heads * vdim + h * vdim + j] = out;
     }
     __syncthreads();      // the buffer is filled again two runs on
