@@ -17,8 +17,10 @@
 //   gdn_scan         the recurrence: the columns of S are independent, so thread (column j, part p)
 //                    keeps DPL rows of column j in registers; the P parts of a column add their
 //                    shares of S^T k and S^T q (both of the matrix before the token's write: the
-//                    read-out after it is g S^T q + (k . q) u) in one round of shuffles.  Tokens are staged through shared memory
-//                    in runs, the next run's copies (cp.async) in flight behind the current one
+//                    read-out after it is g S^T q + (k . q) u) in one round of shuffles, one half of
+//                    the lanes gathering one sum, the other half the other.  Tokens are staged through
+//                    shared memory in runs, the next run's copies (cp.async) in flight behind the current
+//                    one; a token's operands are in registers before the token before it is done
 //   gdn_out_norm     a warp a (token, head): o / rms(o) * gain * scale * silu(gate)
 #include "common.cuh"
 
@@ -114,9 +116,36 @@ __device__ __forceinline__ void gdn_copy4(float* dst, const float* src) {
 }
 
 // qkv: [T, channels] as gdn_prepare wrote it; bg: [T, 2 heads] (beta, then the decay).
-// Block: `cols` columns of one head of one request, P parts a column (cols * P threads).
+// Block: `cols` columns of one head of one request, P parts a column (cols * P = GDN_SCAN_THREADS).
+// Part p of a column owns the rows of the 4-row pieces p, P + p, 2 P + p, ...: the P parts of a column
+// then read P neighbouring 16-byte pieces of k, of q and of the kept matrix at a time.
+#define GDN_SCAN_THREADS 128
+
 template <int DPL>
-__global__ void __launch_bounds__(GDN_THREADS)
+struct GdnToken {
+  float k[DPL], q[DPL], v, beta, decay, kq;
+};
+
+template <int DPL>
+__device__ __forceinline__ void gdn_fetch(GdnToken<DPL>& t, const float* k_s, const float* q_s, const float* v_s,
+                                          const float* b_s, const float* g_s, const float* kq_s, int tok, int dim_p,
+                                          int cols, int P, int part, int col) {
+#pragma unroll
+  for (int e = 0; e < DPL; e += 4) {
+    const int at = tok * dim_p + ((e >> 2) * P + part) * 4;
+    const float4 a = *reinterpret_cast<const float4*>(k_s + at);
+    const float4 b = *reinterpret_cast<const float4*>(q_s + at);
+    t.k[e] = a.x; t.k[e + 1] = a.y; t.k[e + 2] = a.z; t.k[e + 3] = a.w;
+    t.q[e] = b.x; t.q[e + 1] = b.y; t.q[e + 2] = b.z; t.q[e + 3] = b.w;
+  }
+  t.v = v_s[tok * cols + col];
+  t.beta = b_s[tok];
+  t.decay = g_s[tok];
+  t.kq = kq_s[tok];
+}
+
+template <int DPL>
+__global__ void __launch_bounds__(GDN_SCAN_THREADS)
 gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int channels, int groups, int heads,
                 int dim, int vdim, int P, int cols, int run, float* __restrict__ state, long long state_stride,
                 const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ o_out) {
@@ -131,8 +160,8 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
   pdl_wait();
   pdl_launch();
   if (first >= last) return;
-  // a buffer: k [run][dim_p], q [run][dim_p], v [run][cols], beta [run], decay [run]
-  const int per = (run * (2 * dim_p + cols + 2) + 3) / 4 * 4;     // whole 16 bytes: the rows are read as float4
+  // a buffer: k [run][dim_p], q [run][dim_p], v [run][cols], beta [run], decay [run], k . q [run]
+  const int per = (run * (2 * dim_p + cols + 3) + 3) / 4 * 4;     // whole 16 bytes: the rows are read as float4
   for (int i = threadIdx.x; i < 2 * per; i += blockDim.x) gdn_stage[i] = 0.f;   // the padded lanes stay zero
   __syncthreads();
   const int g = h / (heads / groups);
@@ -163,13 +192,16 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   float S[DPL];
-  float* mine = state + (size_t)state_slot[r] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim_p + part * DPL;
+  float* mine = state + (size_t)state_slot[r] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim_p;
 #pragma unroll
   for (int e = 0; e < DPL; e += 4) {
-    const float4 v = live ? *reinterpret_cast<const float4*>(mine + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 v = live ? *reinterpret_cast<const float4*>(mine + ((e >> 2) * P + part) * 4)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
     S[e] = v.x; S[e + 1] = v.y; S[e + 2] = v.z; S[e + 3] = v.w;
   }
   const int n_runs = (last - first + run - 1) / run;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool upper = P > 1 && (part & (P >> 1));     // which of the two sums this lane ends up with
   issue(0, 0);
   for (int c = 0; c < n_runs; ++c) {
     if (c + 1 < n_runs) {
@@ -184,47 +216,55 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
     const float* v_s = q_s + run * dim_p;
     const float* b_s = v_s + run * cols;
     const float* g_s = b_s + run;
+    float* kq_s = const_cast<float*>(g_s) + run;
     const int t0 = first + c * run;
     const int n = min(run, last - t0);
+    // k . q of the run's tokens, a warp a token: it does not wait on the matrix
+    for (int tok = warp; tok < n; tok += GDN_SCAN_THREADS / 32) {
+      float acc = 0.f;
+      for (int l = lane; l < dim; l += 32) acc = fmaf(k_s[tok * dim_p + l], q_s[tok * dim_p + l], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) kq_s[tok] = acc;
+    }
+    __syncthreads();
+    GdnToken<DPL> now, next;
+    gdn_fetch<DPL>(now, k_s, q_s, v_s, b_s, g_s, kq_s, 0, dim_p, cols, P, part, col);
     for (int tok = 0; tok < n; ++tok) {
-      float kk[DPL], qq[DPL];
-#pragma unroll
-      for (int e = 0; e < DPL; e += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(k_s + tok * dim_p + part * DPL + e);
-        const float4 b = *reinterpret_cast<const float4*>(q_s + tok * dim_p + part * DPL + e);
-        kk[e] = a.x; kk[e + 1] = a.y; kk[e + 2] = a.z; kk[e + 3] = a.w;
-        qq[e] = b.x; qq[e + 1] = b.y; qq[e + 2] = b.z; qq[e + 3] = b.w;
-      }
-      const float vj = v_s[tok * cols + col], beta = b_s[tok], decay = g_s[tok];
-      // both read-outs from the matrix as it stands: S'^T q = g S^T q + (k . q) u, so that one round of
-      // shuffles serves the token (the chain from token to token is the sums, the round, u, the update)
-      float dk[2] = {0.f, 0.f}, dq[2] = {0.f, 0.f}, kq = 0.f;
+      // the next token's operands are asked for before this token's sums are waited for
+      if (tok + 1 < n) gdn_fetch<DPL>(next, k_s, q_s, v_s, b_s, g_s, kq_s, tok + 1, dim_p, cols, P, part, col);
+      // both read-outs from the matrix as it stands: S'^T q = g S^T q + (k . q) u
+      float dk[2] = {0.f, 0.f}, dq[2] = {0.f, 0.f};
 #pragma unroll
       for (int e = 0; e < DPL; e += 2) {
-        dk[0] = fmaf(S[e], kk[e], dk[0]);
-        dk[1] = fmaf(S[e + 1], kk[e + 1], dk[1]);
-        dq[0] = fmaf(S[e], qq[e], dq[0]);
-        dq[1] = fmaf(S[e + 1], qq[e + 1], dq[1]);
-        kq = fmaf(kk[e], qq[e], fmaf(kk[e + 1], qq[e + 1], kq));
+        dk[0] = fmaf(S[e], now.k[e], dk[0]);
+        dk[1] = fmaf(S[e + 1], now.k[e + 1], dk[1]);
+        dq[0] = fmaf(S[e], now.q[e], dq[0]);
+        dq[1] = fmaf(S[e + 1], now.q[e + 1], dq[1]);
       }
       float dot = dk[0] + dk[1], read = dq[0] + dq[1];
-      for (int o = P >> 1; o > 0; o >>= 1) {
-        dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        read += __shfl_xor_sync(0xffffffffu, read, o);
-        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      if (P > 1) {
+        // the two sums over a column's P lanes in one round: the lower half of the lanes gathers
+        // S^T k, the upper half S^T q (each hands the other sum over first)
+        float keep = upper ? read : dot;
+        keep += __shfl_xor_sync(0xffffffffu, upper ? dot : read, P >> 1);
+        for (int o = P >> 2; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+        dot = keep;
+        read = keep;
       }
-      const float u = beta * (vj - decay * dot);
-      const float out = fmaf(kq, u, decay * read);
+      float u = now.beta * (now.v - now.decay * dot);          // right in the lower lanes
+      if (P > 1) u = __shfl_sync(0xffffffffu, u, 0, P);
+      const float out = fmaf(now.kq, u, now.decay * read);     // right in the upper lanes (all, where P is 1)
 #pragma unroll
-      for (int e = 0; e < DPL; ++e) S[e] = fmaf(kk[e], u, decay * S[e]);
-      if (live && part == 0) o_out[(size_t)(t0 + tok) * heads * vdim + h * vdim + j] = out;
+      for (int e = 0; e < DPL; ++e) S[e] = fmaf(now.k[e], u, now.decay * S[e]);
+      if (live && part == (P >> 1)) o_out[(size_t)(t0 + tok) * heads * vdim + h * vdim + j] = out;
+      now = next;
     }
     __syncthreads();      // the buffer is filled again two runs on
   }
   if (live) {
 #pragma unroll
     for (int e = 0; e < DPL; e += 4)
-      *reinterpret_cast<float4*>(mine + e) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
+      *reinterpret_cast<float4*>(mine + ((e >> 2) * P + part) * 4) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
   }
 }
 
@@ -240,12 +280,26 @@ __global__ void gdn_out_norm_kernel(const float* __restrict__ o, const TG* __res
   const int t = unit / heads, h = unit % heads;
   if (row_req[t] < 0) return;
   const float* row = o + ((size_t)t * heads + h) * vdim;
+  const TG* gates = gate + (size_t)t * ld + g_at + h * vdim;
+  TO* y = out + ((size_t)t * heads + h) * vdim;
+  if (vdim == 128 && sizeof(TG) == 4 && ((((uintptr_t)row) | ((uintptr_t)gates) | ((uintptr_t)gain)) & 15) == 0 &&
+      (((uintptr_t)y) & 7) == 0) {
+    // a head of 128 lanes: four consecutive lanes a thread, every operand in one 16-byte load
+    const float4 v = *reinterpret_cast<const float4*>(row + lane * 4);
+    const float4 z = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(gates) + lane * 4);
+    const float4 w = *reinterpret_cast<const float4*>(gain + lane * 4);
+    const float ss4 = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    const float inv4 = (1.0f / sqrtf(ss4 / 128.0f + eps)) * scale;
+    y[lane * 4] = from_float<TO>(v.x * inv4 * w.x * (z.x * gdn_sigmoid(z.x)));
+    y[lane * 4 + 1] = from_float<TO>(v.y * inv4 * w.y * (z.y * gdn_sigmoid(z.y)));
+    y[lane * 4 + 2] = from_float<TO>(v.z * inv4 * w.z * (z.z * gdn_sigmoid(z.z)));
+    y[lane * 4 + 3] = from_float<TO>(v.w * inv4 * w.w * (z.w * gdn_sigmoid(z.w)));
+    return;
+  }
   float ss = 0.f;
   for (int l = lane; l < vdim; l += 32) ss += row[l] * row[l];
   ss = warp_sum(ss);
   const float inv = (1.0f / sqrtf(ss / (float)vdim + eps)) * scale;
-  const TG* gates = gate + (size_t)t * ld + g_at + h * vdim;
-  TO* y = out + ((size_t)t * heads + h) * vdim;
   for (int l = lane; l < vdim; l += 32) {
     const float z = to_float(gates[l]);
     y[l] = from_float<TO>(row[l] * inv * gain[l] * (z * gdn_sigmoid(z)));
@@ -253,17 +307,19 @@ __global__ void gdn_out_norm_kernel(const float* __restrict__ o, const TG* __res
 }
 
 // ---- launchers -----------------------------------------------------------------------------------
+// Rows a thread keeps of its column: 8 for heads of up to 32 lanes, 16 up to 128, 32 beyond; and the
+// parts of a column (a power of two).
+static inline int gdn_rows(int dim) { return dim <= 32 ? 8 : dim <= 128 ? 16 : 32; }
 static inline int gdn_parts(int dim, int dpl) {
   int p = 1;
   while (p * dpl < dim) p <<= 1;
   return p;
 }
 
-// Rows of a head's padded state column (the recurrence keeps 8 rows a thread up to dim 256, 32 beyond).
+// Rows of a head's padded state column.
 TOKB200_API int tokb200_gdn_padded_dim(int dim) {
   if (dim <= 0 || dim > 1024) return 0;
-  const int dpl = dim <= 256 ? 8 : 32;
-  return gdn_parts(dim, dpl) * dpl;
+  return gdn_parts(dim, gdn_rows(dim)) * gdn_rows(dim);
 }
 
 TOKB200_API int tokb200_gdn_prepare(const void* proj, int proj_dtype, int ld, int qkv_at, int b_at, int a_at,
@@ -311,21 +367,23 @@ TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, 
     return TOKB200_BAD_SIZE;
   if (((uintptr_t)state & 15) || state_stride % 4) return TOKB200_BAD_ALIGNMENT;
   const int channels = 2 * groups * dim + heads * vdim;
-  const int dpl = dim <= 256 ? 8 : 32;
+  const int dpl = gdn_rows(dim);
   const int P = gdn_parts(dim, dpl);
-  const int cols = GDN_THREADS / P;
+  const int cols = GDN_SCAN_THREADS / P;
   const int dim_p = P * dpl;
   // tokens a run: what two buffers of 48 KB together hold, at most 16
-  int run = (48 * 1024 / 2 / (int)sizeof(float) - 4) / (2 * dim_p + cols + 2);
+  int run = (48 * 1024 / 2 / (int)sizeof(float) - 4) / (2 * dim_p + cols + 3);
   run = run > 16 ? 16 : run;
   if (run < 1) return TOKB200_BAD_SIZE;
-  const size_t smem = (size_t)2 * ((run * (2 * dim_p + cols + 2) + 3) / 4 * 4) * sizeof(float);
+  const size_t smem = (size_t)2 * ((run * (2 * dim_p + cols + 3) + 3) / 4 * 4) * sizeof(float);
   dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
-  if (dpl == 8)
-    return launch_dependent(gdn_scan_kernel<8>, grid, dim3(GDN_THREADS), smem, stream, qkv, bg, channels, groups,
-                            heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out);
-  return launch_dependent(gdn_scan_kernel<32>, grid, dim3(GDN_THREADS), smem, stream, qkv, bg, channels, groups,
-                          heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out);
+#define LAUNCH(D)                                                                                               \
+  return launch_dependent(gdn_scan_kernel<D>, grid, dim3(GDN_SCAN_THREADS), smem, stream, qkv, bg, channels,    \
+                          groups, heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out)
+  if (dpl == 8) LAUNCH(8);
+  if (dpl == 16) LAUNCH(16);
+  LAUNCH(32);
+#undef LAUNCH
 }
 
 TOKB200_API int tokb200_gdn_out_norm(const float* o, const void* gate, int gate_dtype, int ld, int g_at,

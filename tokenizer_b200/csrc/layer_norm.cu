@@ -164,6 +164,106 @@ post_norm_add_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* _
     o[i] = from_float<TO>((xr[i] - mean) * inv * next_gain[i] + next_bias[i]);
 }
 
+// ---- rows whose width is whole 8s: eight consecutive elements a thread, 16-byte loads ----
+__device__ __forceinline__ void ln_load8(const float* p, float v[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+__device__ __forceinline__ void ln_store8(float* p, const float v[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+__device__ __forceinline__ void ln_store8(__nv_bfloat16* p, const float v[8]) {
+  __nv_bfloat162 h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(h);
+}
+
+// adds the term's eight elements at `at`, scaled, to v
+__device__ __forceinline__ void ln_term8(const LnTerm& t, size_t at, float v[8]) {
+  if (t.y == nullptr) return;
+  if (t.bf16) {
+    const uint4 raw = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)t.y + at);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] += f.x * t.scale;
+      v[2 * i + 1] += f.y * t.scale;
+    }
+    return;
+  }
+  float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < t.n_partials; ++s) {
+    float part[8];
+    ln_load8((const float*)t.y + (size_t)s * t.stride + at, part);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum[i] += part[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] += sum[i] * t.scale;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+post_norm_add_rows8_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* __restrict__ gain,
+                           const float* __restrict__ bias, float eps, const float* __restrict__ next_gain,
+                           const float* __restrict__ next_bias, float next_eps, TO* __restrict__ out, int hidden) {
+  __shared__ float scratch[33];
+  // gains and biases are weights: asked for before the wait on the predecessor
+  const int i0 = threadIdx.x * 8;
+  const bool on = i0 < hidden;
+  float g[8], b[8];
+  if (on) {
+    ln_load8(gain + i0, g);
+    ln_load8(bias + i0, b);
+  }
+  pdl_wait();
+  pdl_launch();
+  const size_t base = (size_t)blockIdx.x * hidden + i0;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, xv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (on) {
+    ln_load8(x + base, xv);
+    ln_term8(t1, base, v);
+    ln_term8(t2, base, v);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += v[i];
+  const float mean = block_sum(s, scratch) / (float)hidden;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q += on ? (v[i] - mean) * (v[i] - mean) : 0.f;
+  const float inv = 1.0f / sqrtf(block_sum(q, scratch) / (float)hidden + eps);
+  s = 0.f;
+  if (on) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      xv[i] += (v[i] - mean) * inv * g[i] + b[i];
+      s += xv[i];
+    }
+    ln_store8(x + base, xv);
+  }
+  if (out == nullptr) return;
+  if (on) {
+    ln_load8(next_gain + i0, g);
+    ln_load8(next_bias + i0, b);
+  }
+  const float mean2 = block_sum(s, scratch) / (float)hidden;
+  q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q += on ? (xv[i] - mean2) * (xv[i] - mean2) : 0.f;
+  const float inv2 = 1.0f / sqrtf(block_sum(q, scratch) / (float)hidden + next_eps);
+  if (on) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (xv[i] - mean2) * inv2 * g[i] + b[i];
+    ln_store8(out + base, v);
+  }
+}
+
 __global__ void scaled_sum_kernel(LnTerm t1, LnTerm t2, float* __restrict__ out, size_t n) {
   pdl_wait();
   pdl_launch();
@@ -224,6 +324,19 @@ TOKB200_API int tokb200_post_norm_add(float* x, const void* y1, int y1_dtype, in
     return TOKB200_BAD_DTYPE;
   const LnTerm t1 = ln_make_term(y1, y1_dtype, y1_partials, y1_stride, y1_scale);
   const LnTerm t2 = ln_make_term(y2, y2_dtype, y2_partials, y2_stride, y2_scale);
+  // whole 8s of up to 8,192 elements, everything on 16 bytes: eight elements a thread
+  const uintptr_t all = (uintptr_t)x | (uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)gain | (uintptr_t)bias |
+                        (uintptr_t)next_gain | (uintptr_t)next_bias | (uintptr_t)out;
+  if (hidden % 8 == 0 && hidden <= 8192 && (all & 15) == 0 && y1_stride % 4 == 0 && y2_stride % 4 == 0) {
+    const int threads8 = ((hidden / 8 + 31) / 32) * 32;
+    if (out == nullptr || out_dtype == TOKB200_F32)
+      return launch_dependent(post_norm_add_rows8_kernel<float>, dim3(n_rows), dim3(threads8), 0, stream, x, t1, t2,
+                              gain, bias, eps, next_gain, next_bias, next_eps, (float*)out, hidden);
+    if (out_dtype == TOKB200_BF16)
+      return launch_dependent(post_norm_add_rows8_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads8), 0, stream, x,
+                              t1, t2, gain, bias, eps, next_gain, next_bias, next_eps, (__nv_bfloat16*)out, hidden);
+    return TOKB200_BAD_DTYPE;
+  }
   const int threads = ln_threads(hidden);
   if (out == nullptr || out_dtype == TOKB200_F32)
     return launch_dependent(post_norm_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, t1, t2, gain,

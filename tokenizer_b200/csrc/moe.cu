@@ -27,6 +27,16 @@ moe_route_kernel(const TI* __restrict__ h, const float* __restrict__ w, int hidd
   for (int e = warp; e < experts + shared; e += blockDim.x >> 5) {
     const float* we = w + (size_t)e * hidden;
     float acc = 0.f;
+    if (hidden % 128 == 0 && ((((uintptr_t)row) | ((uintptr_t)we)) & 15) == 0) {
+      // four consecutive elements a lane and trip: 16-byte loads of the router's row
+      for (int i = lane * 4; i < hidden; i += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(we + i);
+        acc = fmaf(to_float(row[i]), wv.x, acc);
+        acc = fmaf(to_float(row[i + 1]), wv.y, acc);
+        acc = fmaf(to_float(row[i + 2]), wv.z, acc);
+        acc = fmaf(to_float(row[i + 3]), wv.w, acc);
+      }
+    } else
     for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(row[i]), we[i], acc);
     acc = warp_sum(acc);
     if (lane == 0) z[e] = acc;
@@ -82,6 +92,37 @@ __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restric
   }
 }
 
+// bfloat16, inner and expert widths in whole 8s: eight consecutive lanes (one expert's) a thread
+__global__ void moe_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ share,
+                                       __nv_bfloat16* __restrict__ out, int inner, int experts, int ff, int shared,
+                                       int act, size_t n8) {
+  pdl_wait();
+  pdl_launch();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const int per_row = inner / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const size_t t = i / per_row;
+    const int c = (int)(i % per_row) * 8;
+    const int e = c < experts * ff ? c / ff : experts;
+    const float w = share[t * (experts + shared) + e];
+    uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {
+      const uint4 graw = *reinterpret_cast<const uint4*>(gu + t * 2 * inner + c);
+      const uint4 uraw = *reinterpret_cast<const uint4*>(gu + t * 2 * inner + inner + c);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+      __nv_bfloat162 h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        h[k] = __floats2bfloat162_rn(gate_activation(act, g.x) * u.x * w, gate_activation(act, g.y) * u.y * w);
+      }
+      packed = *reinterpret_cast<const uint4*>(h);
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = packed;
+  }
+}
+
 TOKB200_API int tokb200_moe_route(const void* h, int h_dtype, const float* w, int hidden, int experts, int top,
                                   int shared, float* share, int n_rows, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
@@ -109,6 +150,12 @@ TOKB200_API int tokb200_moe_gate(const void* gu, const float* share, void* out, 
   if (dtype == TOKB200_F32)
     return launch_dependent(moe_gate_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, share, (float*)out,
                             inner, experts, ff, shared, act, n);
+  if (dtype == TOKB200_BF16 && inner % 8 == 0 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    const size_t n8 = n / 8, blocks8 = (n8 + 255) / 256;
+    return launch_dependent(moe_gate_bf16x8_kernel, dim3((unsigned)(blocks8 < 65535 ? blocks8 : 65535)), dim3(256), 0,
+                            stream, (const __nv_bfloat16*)gu, share, (__nv_bfloat16*)out, inner, experts, ff, shared,
+                            act, n8);
+  }
   if (dtype == TOKB200_BF16)
     return launch_dependent(moe_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu,
                             share, (__nv_bfloat16*)out, inner, experts, ff, shared, act, n);

@@ -1158,10 +1158,11 @@ def stream_inject(x: torch.Tensor, other: Optional[torch.Tensor], vector: Option
 # ---- the gated delta rule ----
 def gdn_padded_dim(dim: int) -> int:
     """Rows of a head's state column as the recurrence keeps it (dim rounded up to what its threads
-    hold: whole 8s times a power of two up to 256, whole 32s beyond); 0: a size it does not take."""
+    hold: a power of two times 8 rows for heads of up to 32 lanes, 16 up to 128, 32 beyond); 0: a size it
+    does not take."""
     if not 0 < dim <= 1024:
         return 0
-    per = 8 if dim <= 256 else 32
+    per = 8 if dim <= 32 else 16 if dim <= 128 else 32
     parts = 1
     while parts * per < dim:
         parts *= 2
