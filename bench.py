@@ -985,7 +985,7 @@ def run_katopel(args):
     slot_floats = -(-(conv_off + (taps - 1) * channels) // 4) * 4
     proj = rnd(T, channels + 2 * heads + heads * vdim)
     conv, a_log, dt_bias = rnd(channels, taps), rnd(heads), rnd(heads)
-    qkv, bg = torch.empty(T, channels, device=dev), torch.empty(T, 2 * heads, device=dev)
+    qkv, bg = torch.empty(T, channels, device=dev), torch.empty(T, 2 * heads + groups, device=dev)
     o = torch.empty(T, heads * vdim, device=dev)
     y16 = torch.empty(T, heads * vdim, dtype=torch.bfloat16, device=dev)
     gain_v = torch.ones(vdim, device=dev)

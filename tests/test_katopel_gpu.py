@@ -155,7 +155,7 @@ def test_the_delta_rule_in_portions_carries_matrices_and_kept_inputs(groups, hea
         sub = proj[idx].contiguous()
         row_req = ints(r for r in range(len(who)) for _ in range(spans[r + 1] - spans[r]))
         qkv = torch.empty(len(rows), channels, device=DEV)
-        bg = torch.empty(len(rows), 2 * heads, device=DEV)
+        bg = torch.empty(len(rows), 2 * heads + groups, device=DEV)
         o.gdn_prepare(sub, extra, extra + channels, extra + channels + heads, groups, heads, dim, vdim, taps, conv,
                       a_log, dt_bias, state, conv_off, row_req, ints(spans), ints(who), qkv, bg)
         got = torch.empty(len(rows), heads * vdim, device=DEV)
@@ -183,7 +183,7 @@ def test_a_token_written_far_back_is_read_from_the_matrix():
     o = ops()
     dim, vdim, total = 32, 16, 901
     qkv = torch.zeros(total, 2 * dim + vdim, device=DEV)
-    bg = torch.ones(total, 2, device=DEV)                  # beta 1, decay 1
+    bg = torch.ones(total, 3, device=DEV)                  # beta 1, decay 1, and q . k (set below)
     for t in range(total):
         qkv[t, dim + 1 + t % (dim - 1)] = 1.0              # keys e1 .. e31 in turn
         qkv[t, t % dim] = 1.0
@@ -193,6 +193,7 @@ def test_a_token_written_far_back_is_read_from_the_matrix():
     qkv[3, 2 * dim:] = marker
     qkv[900, :dim] = 0.0
     qkv[900, 0] = 1.0                                      # token 900 reads along e0
+    bg[:, 2] = (qkv[:, :dim] * qkv[:, dim:2 * dim]).sum(dim=1)
     state = torch.zeros(2, vdim * o.gdn_padded_dim(dim), device=DEV)
     out = torch.empty(total, vdim, device=DEV)
     at = 0

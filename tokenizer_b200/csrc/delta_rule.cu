@@ -19,8 +19,8 @@
 //                    shares of S^T k and S^T q (both of the matrix before the token's write: the
 //                    read-out after it is g S^T q + (k . q) u) in one round of shuffles, one half of
 //                    the lanes gathering one sum, the other half the other.  Tokens are staged through
-//                    shared memory in runs, the next run's copies (cp.async) in flight behind the current
-//                    one; a token's operands are in registers before the token before it is done
+//                    shared memory in runs by a warp of its own (cp.async), a run ahead of the warps
+//                    that compute; a token's operands are in registers before the token before it is done
 //   gdn_out_norm     a warp a (token, head): o / rms(o) * gain * scale * silu(gate)
 #include "common.cuh"
 
@@ -41,7 +41,7 @@ gdn_prepare_kernel(const TI* __restrict__ proj, int ld, int qkv_at, int b_at, in
                    int conv_off, const int* __restrict__ row_req, const int* __restrict__ q_start,
                    const int* __restrict__ state_slot, float q_scale, float* __restrict__ qkv_out,
                    float* __restrict__ bg_out) {
-  extern __shared__ float gdn_vals[];      // channels
+  extern __shared__ float gdn_vals[];      // channels, then 2 groups scales
   const int t = blockIdx.x;
   const int channels = 2 * groups * dim + heads * vdim;
   const int r = row_req[t];
@@ -63,19 +63,29 @@ gdn_prepare_kernel(const TI* __restrict__ proj, int ld, int qkv_at, int b_at, in
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   float* out = qkv_out + (size_t)t * channels;
+  float* scales = gdn_vals + channels;
   for (int h = warp; h < 2 * groups; h += warps) {   // q heads, then k heads
     float ss = 0.f;
     for (int l = lane; l < dim; l += 32) ss += gdn_vals[h * dim + l] * gdn_vals[h * dim + l];
     ss = warp_sum(ss);
     const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (h < groups ? q_scale : 1.0f);
     for (int l = lane; l < dim; l += 32) out[h * dim + l] = gdn_vals[h * dim + l] * inv;
+    if (lane == 0) scales[h] = inv;
+  }
+  __syncthreads();
+  // q . k of every group, as the recurrence's read-out wants it (of the scaled unit vectors)
+  for (int g = warp; g < groups; g += warps) {
+    float dot = 0.f;
+    for (int l = lane; l < dim; l += 32) dot = fmaf(gdn_vals[g * dim + l], gdn_vals[(groups + g) * dim + l], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) bg_out[(size_t)t * (2 * heads + groups) + 2 * heads + g] = dot * scales[g] * scales[groups + g];
   }
   for (int c = 2 * groups * dim + threadIdx.x; c < channels; c += blockDim.x) out[c] = gdn_vals[c];
   for (int h = threadIdx.x; h < heads; h += blockDim.x) {
     const float b = to_float(proj[(size_t)t * ld + b_at + h]);
     const float a = to_float(proj[(size_t)t * ld + a_at + h]) + dt_bias[h];
-    bg_out[(size_t)t * 2 * heads + h] = gdn_sigmoid(b);
-    bg_out[(size_t)t * 2 * heads + heads + h] = expf(-expf(a_log[h]) * gdn_softplus(a));
+    bg_out[(size_t)t * (2 * heads + groups) + h] = gdn_sigmoid(b);
+    bg_out[(size_t)t * (2 * heads + groups) + heads + h] = expf(-expf(a_log[h]) * gdn_softplus(a));
   }
 }
 
@@ -115,10 +125,11 @@ __device__ __forceinline__ void gdn_copy4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(to), "l"(src) : "memory");
 }
 
-// qkv: [T, channels] as gdn_prepare wrote it; bg: [T, 2 heads] (beta, then the decay).
-// Block: `cols` columns of one head of one request, P parts a column (cols * P = GDN_SCAN_THREADS).
-// Part p of a column owns the rows of the 4-row pieces p, P + p, 2 P + p, ...: the P parts of a column
-// then read P neighbouring 16-byte pieces of k, of q and of the kept matrix at a time.
+// qkv: [T, channels] as gdn_prepare wrote it; bg: [T, 2 heads + groups] (beta, the decay, q . k).
+// Block: `cols` columns of one head of one request, P parts a column (cols * P = GDN_SCAN_THREADS
+// threads that compute) and one more warp that only stages tokens.  Part p of a column owns the rows of
+// the 4-row pieces p, P + p, 2 P + p, ...: the P parts of a column then read P neighbouring 16-byte
+// pieces of k, of q and of the kept matrix at a time.
 #define GDN_SCAN_THREADS 128
 
 template <int DPL>
@@ -127,25 +138,29 @@ struct GdnToken {
 };
 
 template <int DPL>
-__device__ __forceinline__ void gdn_fetch(GdnToken<DPL>& t, const float* k_s, const float* q_s, const float* v_s,
-                                          const float* b_s, const float* g_s, const float* kq_s, int tok, int dim_p,
-                                          int cols, int P, int part, int col) {
+__device__ __forceinline__ void gdn_fetch(GdnToken<DPL>& t, const float* k_mine, const float* q_mine,
+                                          const float* v_mine, const float* b_s, int tok, int dim_p, int cols,
+                                          int piece, int run) {
 #pragma unroll
   for (int e = 0; e < DPL; e += 4) {
-    const int at = tok * dim_p + ((e >> 2) * P + part) * 4;
-    const float4 a = *reinterpret_cast<const float4*>(k_s + at);
-    const float4 b = *reinterpret_cast<const float4*>(q_s + at);
+    const float4 a = *reinterpret_cast<const float4*>(k_mine + tok * dim_p + (e >> 2) * piece);
+    const float4 b = *reinterpret_cast<const float4*>(q_mine + tok * dim_p + (e >> 2) * piece);
     t.k[e] = a.x; t.k[e + 1] = a.y; t.k[e + 2] = a.z; t.k[e + 3] = a.w;
     t.q[e] = b.x; t.q[e + 1] = b.y; t.q[e + 2] = b.z; t.q[e + 3] = b.w;
   }
-  t.v = v_s[tok * cols + col];
+  t.v = v_mine[tok * cols];
   t.beta = b_s[tok];
-  t.decay = g_s[tok];
-  t.kq = kq_s[tok];
+  t.decay = b_s[run + tok];
+  t.kq = b_s[2 * run + tok];
+}
+
+__device__ __forceinline__ void gdn_copy16(float* dst, const float* src) {
+  const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(src) : "memory");
 }
 
 template <int DPL>
-__global__ void __launch_bounds__(GDN_SCAN_THREADS)
+__global__ void __launch_bounds__(GDN_SCAN_THREADS + 32)
 gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int channels, int groups, int heads,
                 int dim, int vdim, int P, int cols, int run, float* __restrict__ state, long long state_stride,
                 const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ o_out) {
@@ -153,9 +168,6 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
   const int dim_p = P * DPL;
   const int r = blockIdx.z, h = blockIdx.y;
   const int col0 = blockIdx.x * cols;
-  const int part = threadIdx.x % P, col = threadIdx.x / P;
-  const int j = col0 + col;
-  const bool live = j < vdim;
   const int first = q_start[r], last = q_start[r + 1];
   pdl_wait();
   pdl_launch();
@@ -167,104 +179,125 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
   const int g = h / (heads / groups);
   const int k_col = (groups + g) * dim, q_col = g * dim, v_col = 2 * groups * dim + h * vdim + col0;
   const int n_cols = min(cols, vdim - col0);
-  auto issue = [&](int c, int buf) {
-    float* k_s = gdn_stage + (size_t)buf * per;
-    float* q_s = k_s + run * dim_p;
-    float* v_s = q_s + run * dim_p;
-    float* b_s = v_s + run * cols;
-    float* g_s = b_s + run;
-    const int t0 = first + c * run;
-    const int n = min(run, last - t0);
-    for (int i = threadIdx.x; i < n * dim; i += blockDim.x) {
-      const int tok = i / dim, l = i % dim;
-      const float* row = qkv + (size_t)(t0 + tok) * channels;
-      gdn_copy4(&k_s[tok * dim_p + l], row + k_col + l);
-      gdn_copy4(&q_s[tok * dim_p + l], row + q_col + l);
+  const int n_runs = (last - first + run - 1) / run;
+  const int n_bg = 2 * heads + groups;
+
+  if (threadIdx.x >= GDN_SCAN_THREADS) {
+    // ---- the staging warp: run c + 1 lands while the others work through run c ----
+    const int lane = threadIdx.x - GDN_SCAN_THREADS;
+    // 16-byte copies where every row piece starts on 16 bytes
+    const bool wide = dim % 4 == 0 && channels % 4 == 0 && k_col % 4 == 0 && q_col % 4 == 0 &&
+                      (((uintptr_t)qkv) & 15) == 0;
+    for (int c = 0; c <= n_runs; ++c) {
+      if (c < n_runs) {
+        float* k_s = gdn_stage + (size_t)(c & 1) * per;
+        float* q_s = k_s + run * dim_p;
+        float* v_s = q_s + run * dim_p;
+        float* b_s = v_s + run * cols;
+        const int t0 = first + c * run;
+        const int n = min(run, last - t0);
+        if (wide) {
+          const int quads = dim >> 2;
+          for (int i = lane; i < n * quads; i += 32) {
+            const int tok = i / quads, l = (i - tok * quads) * 4;
+            const float* row = qkv + (size_t)(t0 + tok) * channels;
+            gdn_copy16(&k_s[tok * dim_p + l], row + k_col + l);
+            gdn_copy16(&q_s[tok * dim_p + l], row + q_col + l);
+          }
+        } else {
+          for (int i = lane; i < n * dim; i += 32) {
+            const int tok = i / dim, l = i - tok * dim;
+            const float* row = qkv + (size_t)(t0 + tok) * channels;
+            gdn_copy4(&k_s[tok * dim_p + l], row + k_col + l);
+            gdn_copy4(&q_s[tok * dim_p + l], row + q_col + l);
+          }
+        }
+        for (int i = lane; i < n * n_cols; i += 32) {
+          const int tok = i / n_cols, l = i - tok * n_cols;
+          gdn_copy4(&v_s[tok * cols + l], qkv + (size_t)(t0 + tok) * channels + v_col + l);
+        }
+        for (int tok = lane; tok < n; tok += 32) {
+          const float* row = bg + (size_t)(t0 + tok) * n_bg;
+          gdn_copy4(&b_s[tok], row + h);
+          gdn_copy4(&b_s[run + tok], row + heads + h);
+          gdn_copy4(&b_s[2 * run + tok], row + 2 * heads + g);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      __syncthreads();      // run c is in place; everybody is done with run c - 1
     }
-    for (int i = threadIdx.x; i < n * n_cols; i += blockDim.x) {
-      const int tok = i / n_cols, l = i % n_cols;
-      gdn_copy4(&v_s[tok * cols + l], qkv + (size_t)(t0 + tok) * channels + v_col + l);
-    }
-    for (int tok = threadIdx.x; tok < n; tok += blockDim.x) {
-      gdn_copy4(&b_s[tok], bg + (size_t)(t0 + tok) * 2 * heads + h);
-      gdn_copy4(&g_s[tok], bg + (size_t)(t0 + tok) * 2 * heads + heads + h);
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
+    return;
+  }
+
+  const int part = threadIdx.x % P, col = threadIdx.x / P;
+  const int j = col0 + col;
+  const bool live = j < vdim;
+  const int piece = P * 4;
   float S[DPL];
-  float* mine = state + (size_t)state_slot[r] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim_p;
+  float* mine = state + (size_t)state_slot[r] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim_p + part * 4;
 #pragma unroll
   for (int e = 0; e < DPL; e += 4) {
-    const float4 v = live ? *reinterpret_cast<const float4*>(mine + ((e >> 2) * P + part) * 4)
-                          : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 v = live ? *reinterpret_cast<const float4*>(mine + (e >> 2) * piece) : make_float4(0.f, 0.f, 0.f, 0.f);
     S[e] = v.x; S[e + 1] = v.y; S[e + 2] = v.z; S[e + 3] = v.w;
   }
-  const int n_runs = (last - first + run - 1) / run;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool upper = P > 1 && (part & (P >> 1));     // which of the two sums this lane ends up with
-  issue(0, 0);
-  for (int c = 0; c < n_runs; ++c) {
-    if (c + 1 < n_runs) {
-      issue(c + 1, (c + 1) & 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+  float* o_mine = o_out + (size_t)first * heads * vdim + h * vdim + j;
+  const bool writes = live && part == (P >> 1);
+
+  auto step = [&](const GdnToken<DPL>& t, int row) {
+    // both read-outs from the matrix as it stands: S'^T q = g S^T q + (k . q) u
+    float dk[2] = {0.f, 0.f}, dq[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < DPL; e += 2) {
+      dk[0] = fmaf(S[e], t.k[e], dk[0]);
+      dk[1] = fmaf(S[e + 1], t.k[e + 1], dk[1]);
+      dq[0] = fmaf(S[e], t.q[e], dq[0]);
+      dq[1] = fmaf(S[e + 1], t.q[e + 1], dq[1]);
     }
-    __syncthreads();
+    float dot = dk[0] + dk[1], read = dq[0] + dq[1];
+    if (P > 1) {
+      // the two sums over a column's P lanes in one round: the lower half of the lanes gathers
+      // S^T k, the upper half S^T q (each hands the other sum over first)
+      float keep = upper ? read : dot;
+      keep += __shfl_xor_sync(0xffffffffu, upper ? dot : read, P >> 1);
+      for (int o = P >> 2; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+      dot = keep;
+      read = keep;
+    }
+    float u = t.beta * (t.v - t.decay * dot);              // right in the lower lanes
+    if (P > 1) u = __shfl_sync(0xffffffffu, u, 0, P);
+    const float out = fmaf(t.kq, u, t.decay * read);       // right in the upper lanes (all, where P is 1)
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) S[e] = fmaf(t.k[e], u, t.decay * S[e]);
+    if (writes) o_mine[(size_t)row * heads * vdim] = out;
+  };
+
+  __syncthreads();          // run 0 is in place
+  for (int c = 0; c < n_runs; ++c) {
     const float* k_s = gdn_stage + (size_t)(c & 1) * per;
     const float* q_s = k_s + run * dim_p;
     const float* v_s = q_s + run * dim_p;
     const float* b_s = v_s + run * cols;
-    const float* g_s = b_s + run;
-    float* kq_s = const_cast<float*>(g_s) + run;
-    const int t0 = first + c * run;
-    const int n = min(run, last - t0);
-    // k . q of the run's tokens, a warp a token: it does not wait on the matrix
-    for (int tok = warp; tok < n; tok += GDN_SCAN_THREADS / 32) {
-      float acc = 0.f;
-      for (int l = lane; l < dim; l += 32) acc = fmaf(k_s[tok * dim_p + l], q_s[tok * dim_p + l], acc);
-      acc = warp_sum(acc);
-      if (lane == 0) kq_s[tok] = acc;
-    }
-    __syncthreads();
-    GdnToken<DPL> now, next;
-    gdn_fetch<DPL>(now, k_s, q_s, v_s, b_s, g_s, kq_s, 0, dim_p, cols, P, part, col);
-    for (int tok = 0; tok < n; ++tok) {
-      // the next token's operands are asked for before this token's sums are waited for
-      if (tok + 1 < n) gdn_fetch<DPL>(next, k_s, q_s, v_s, b_s, g_s, kq_s, tok + 1, dim_p, cols, P, part, col);
-      // both read-outs from the matrix as it stands: S'^T q = g S^T q + (k . q) u
-      float dk[2] = {0.f, 0.f}, dq[2] = {0.f, 0.f};
-#pragma unroll
-      for (int e = 0; e < DPL; e += 2) {
-        dk[0] = fmaf(S[e], now.k[e], dk[0]);
-        dk[1] = fmaf(S[e + 1], now.k[e + 1], dk[1]);
-        dq[0] = fmaf(S[e], now.q[e], dq[0]);
-        dq[1] = fmaf(S[e + 1], now.q[e + 1], dq[1]);
+    const float* k_mine = k_s + part * 4, *q_mine = q_s + part * 4, *v_mine = v_s + col;
+    const int n = min(run, last - first - c * run);
+    // a token's operands are asked for before the sums of the token before it are waited for
+    GdnToken<DPL> even, odd;
+    gdn_fetch<DPL>(even, k_mine, q_mine, v_mine, b_s, 0, dim_p, cols, piece, run);
+    for (int tok = 0; tok < n; tok += 2) {
+      if (tok + 1 < n) gdn_fetch<DPL>(odd, k_mine, q_mine, v_mine, b_s, tok + 1, dim_p, cols, piece, run);
+      step(even, c * run + tok);
+      if (tok + 1 < n) {
+        if (tok + 2 < n) gdn_fetch<DPL>(even, k_mine, q_mine, v_mine, b_s, tok + 2, dim_p, cols, piece, run);
+        step(odd, c * run + tok + 1);
       }
-      float dot = dk[0] + dk[1], read = dq[0] + dq[1];
-      if (P > 1) {
-        // the two sums over a column's P lanes in one round: the lower half of the lanes gathers
-        // S^T k, the upper half S^T q (each hands the other sum over first)
-        float keep = upper ? read : dot;
-        keep += __shfl_xor_sync(0xffffffffu, upper ? dot : read, P >> 1);
-        for (int o = P >> 2; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-        dot = keep;
-        read = keep;
-      }
-      float u = now.beta * (now.v - now.decay * dot);          // right in the lower lanes
-      if (P > 1) u = __shfl_sync(0xffffffffu, u, 0, P);
-      const float out = fmaf(now.kq, u, now.decay * read);     // right in the upper lanes (all, where P is 1)
-#pragma unroll
-      for (int e = 0; e < DPL; ++e) S[e] = fmaf(now.k[e], u, now.decay * S[e]);
-      if (live && part == (P >> 1)) o_out[(size_t)(t0 + tok) * heads * vdim + h * vdim + j] = out;
-      now = next;
     }
-    __syncthreads();      // the buffer is filled again two runs on
+    __syncthreads();        // done with run c; run c + 1 is in place
   }
   if (live) {
 #pragma unroll
     for (int e = 0; e < DPL; e += 4)
-      *reinterpret_cast<float4*>(mine + ((e >> 2) * P + part) * 4) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
+      *reinterpret_cast<float4*>(mine + (e >> 2) * piece) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
   }
 }
 
@@ -309,7 +342,15 @@ __global__ void gdn_out_norm_kernel(const float* __restrict__ o, const TG* __res
 // ---- launchers -----------------------------------------------------------------------------------
 // Rows a thread keeps of its column: 8 for heads of up to 32 lanes, 16 up to 128, 32 beyond; and the
 // parts of a column (a power of two).
-static inline int gdn_rows(int dim) { return dim <= 32 ? 8 : dim <= 128 ? 16 : 32; }
+static inline int gdn_rows(int dim) {
+  static const int forced = [] {                     // TOKB200_GDN_ROWS=8|16|32: another split, for measurements
+    const char* v = getenv("TOKB200_GDN_ROWS");
+    const int n = v ? atoi(v) : 0;
+    return (n == 8 || n == 16 || n == 32) ? n : 0;
+  }();
+  if (forced && (dim + forced - 1) / forced <= 32) return forced;
+  return dim <= 32 ? 8 : dim <= 128 ? 16 : 32;
+}
 static inline int gdn_parts(int dim, int dpl) {
   int p = 1;
   while (p * dpl < dim) p <<= 1;
@@ -332,7 +373,7 @@ TOKB200_API int tokb200_gdn_prepare(const void* proj, int proj_dtype, int ld, in
       n_requests > 65535)
     return TOKB200_BAD_SIZE;
   const int channels = 2 * groups * dim + heads * vdim;
-  const size_t smem = (size_t)channels * sizeof(float);
+  const size_t smem = (size_t)(channels + 2 * groups) * sizeof(float);
   if (smem > 48 * 1024) return TOKB200_BAD_SIZE;
   const float q_scale = 1.0f / sqrtf((float)dim);
   int status;
@@ -378,7 +419,7 @@ TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, 
   const size_t smem = (size_t)2 * ((run * (2 * dim_p + cols + 3) + 3) / 4 * 4) * sizeof(float);
   dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
 #define LAUNCH(D)                                                                                               \
-  return launch_dependent(gdn_scan_kernel<D>, grid, dim3(GDN_SCAN_THREADS), smem, stream, qkv, bg, channels,    \
+  return launch_dependent(gdn_scan_kernel<D>, grid, dim3(GDN_SCAN_THREADS + 32), smem, stream, qkv, bg, channels, \
                           groups, heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out)
   if (dpl == 8) LAUNCH(8);
   if (dpl == 16) LAUNCH(16);

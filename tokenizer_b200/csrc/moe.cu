@@ -28,13 +28,22 @@ moe_route_kernel(const TI* __restrict__ h, const float* __restrict__ w, int hidd
     const float* we = w + (size_t)e * hidden;
     float acc = 0.f;
     if (hidden % 128 == 0 && ((((uintptr_t)row) | ((uintptr_t)we)) & 15) == 0) {
-      // four consecutive elements a lane and trip: 16-byte loads of the router's row
+      // four consecutive elements a lane and trip: one load of the input's, one of the router's row
       for (int i = lane * 4; i < hidden; i += 128) {
         const float4 wv = *reinterpret_cast<const float4*>(we + i);
-        acc = fmaf(to_float(row[i]), wv.x, acc);
-        acc = fmaf(to_float(row[i + 1]), wv.y, acc);
-        acc = fmaf(to_float(row[i + 2]), wv.z, acc);
-        acc = fmaf(to_float(row[i + 3]), wv.w, acc);
+        float4 hv;
+        if (sizeof(TI) == 4) {
+          hv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + i);
+        } else {
+          const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(row) + i);
+          const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+          const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+          hv = make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+        acc = fmaf(hv.x, wv.x, acc);
+        acc = fmaf(hv.y, wv.y, acc);
+        acc = fmaf(hv.z, wv.z, acc);
+        acc = fmaf(hv.w, wv.w, acc);
       }
     } else
     for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(row[i]), we[i], acc);

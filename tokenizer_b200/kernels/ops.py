@@ -1160,13 +1160,7 @@ def gdn_padded_dim(dim: int) -> int:
     """Rows of a head's state column as the recurrence keeps it (dim rounded up to what its threads
     hold: a power of two times 8 rows for heads of up to 32 lanes, 16 up to 128, 32 beyond); 0: a size it
     does not take."""
-    if not 0 < dim <= 1024:
-        return 0
-    per = 8 if dim <= 32 else 16 if dim <= 128 else 32
-    parts = 1
-    while parts * per < dim:
-        parts *= 2
-    return parts * per
+    return int(_lib("delta_rule").tokb200_gdn_padded_dim(_i(dim)))
 
 
 def gdn_prepare(proj: torch.Tensor, qkv_at: int, b_at: int, a_at: int, groups: int, heads: int, dim: int, vdim: int,
@@ -1174,12 +1168,13 @@ def gdn_prepare(proj: torch.Tensor, qkv_at: int, b_at: int, a_at: int, groups: i
                 qkv_out: torch.Tensor, bg_out: torch.Tensor) -> None:
     """Short convolution + silu of q, k, v (from `proj`'s columns qkv_at ..), unit vectors for q (times
     dim^-1/2) and k, beta = sigmoid(proj[b_at ..]) and the decay exp(-exp(a_log) softplus(proj[a_at ..] +
-    dt_bias)) -> `qkv_out` float32 [T, channels], `bg_out` float32 [T, 2 heads]; then the convolution's
+    dt_bias)) and q . k of every group -> `qkv_out` float32 [T, channels], `bg_out` float32 [T, 2 heads + groups]
+    (beta, the decay, q . k); then the convolution's
     kept inputs in `state` (float32 [slots, n], at `conv_off` in a slot) move on by the step's rows."""
     channels = 2 * groups * dim + heads * vdim
     n = proj.shape[0]
     if state.dtype != torch.float32 or state.dim() != 2 or tuple(qkv_out.shape) != (n, channels) or \
-            tuple(bg_out.shape) != (n, 2 * heads) or qkv_out.dtype != torch.float32 or bg_out.dtype != torch.float32 or \
+            tuple(bg_out.shape) != (n, 2 * heads + groups) or qkv_out.dtype != torch.float32 or bg_out.dtype != torch.float32 or \
             conv_w.numel() != channels * taps or conv_off + (taps - 1) * channels > state.shape[1]:
         raise ValueError("gdn_prepare: sizes of the state, the taps or the outputs disagree")
     _check(_lib("delta_rule").tokb200_gdn_prepare(
@@ -1196,7 +1191,8 @@ def gdn_scan(qkv: torch.Tensor, bg: torch.Tensor, groups: int, heads: int, dim: 
     ([heads, vdim, gdn_padded_dim(dim)]) at the start of a slot; `o_out` float32 [T, heads * vdim]."""
     n = qkv.shape[0]
     if state.dtype != torch.float32 or o_out.dtype != torch.float32 or tuple(o_out.shape) != (n, heads * vdim) or \
-            qkv.shape[1] != 2 * groups * dim + heads * vdim or heads * vdim * gdn_padded_dim(dim) > state.shape[1]:
+            qkv.shape[1] != 2 * groups * dim + heads * vdim or heads * vdim * gdn_padded_dim(dim) > state.shape[1] or \
+            tuple(bg.shape) != (n, 2 * heads + groups) or bg.dtype != torch.float32:
         raise ValueError("gdn_scan: sizes of the state or the outputs disagree")
     _check(_lib("delta_rule").tokb200_gdn_scan(
         _ptr(qkv), _ptr(bg), _i(groups), _i(heads), _i(dim), _i(vdim), _ptr(state), _ll(state.shape[1]),

@@ -180,7 +180,7 @@ class GatedDeltaNet:
         the output projection)."""
         n, c, h = ctx.n_tokens, self.channels, self.heads
         qkv = torch.empty((n, c), dtype=torch.float32, device=proj.device)
-        bg = torch.empty((n, 2 * h), dtype=torch.float32, device=proj.device)
+        bg = torch.empty((n, 2 * h + self.groups), dtype=torch.float32, device=proj.device)
         ops.gdn_prepare(proj, at, at + c, at + c + h, self.groups, h, self.dim, self.vdim, self.taps, self.conv_w,
                         self.a_log, self.dt_bias, cache.state, self.conv_off, ctx.row_req, ctx.q_start,
                         ctx.state_slot, qkv, bg)
