@@ -177,6 +177,46 @@ def test_the_delta_rule_in_portions_carries_matrices_and_kept_inputs(groups, hea
     assert torch.all(state[1] == 7.0) and torch.all(state[4] == 0.0)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("groups,heads,dim,vdim,taps", [(2, 4, 16, 64, 4), (1, 2, 128, 128, 4), (3, 3, 64, 32, 2),
+                                                         (1, 1, 40, 96, 1), (2, 2, 260, 8, 3)])
+def test_a_step_of_single_tokens_in_one_kernel(groups, heads, dim, vdim, taps, out_dtype):
+    """Token by token through `gdn_step` (three requests, one of them absent from some steps, an idle row of a
+    padded step) against the kernels for portions fed the same rows: outputs, matrices and kept inputs."""
+    o = ops()
+    assert o.gdn_step_supported(dim, vdim)
+    steps, extra = 7, 5
+    channels = 2 * groups * dim + heads * vdim
+    padded = o.gdn_padded_dim(dim)
+    conv_off = heads * vdim * padded
+    floats = -(-(conv_off + (taps - 1) * channels) // 4) * 4
+    conv = rnd(channels, taps, seed=71, scale=0.7)
+    a_log, dt_bias, gain = rnd(heads, seed=72, scale=0.5), rnd(heads, seed=73, scale=0.5) - 1.0, rnd(vdim, seed=74) + 1.0
+    one, many = torch.zeros(4, floats, device=DEV), torch.zeros(4, floats, device=DEV)
+    width = extra + channels + 2 * heads + heads * vdim
+    for step in range(steps):
+        present = [0, 1, 2] if step % 3 else [0, 2]
+        slots = [3, 0, 1]
+        n = len(present) + 1                                                    # the last row is idle
+        proj = rnd(n, width, seed=80 + step, scale=1.5)
+        row_req, spans = ints(list(range(len(present))) + [-1]), ints(list(range(len(present) + 1)) + [len(present)])
+        who = ints([slots[r] for r in present] + [0])
+        got = torch.full((n, heads * vdim), float("nan"), dtype=out_dtype, device=DEV)
+        o.gdn_step(proj, extra, extra + channels, extra + channels + heads, extra + channels + 2 * heads, groups, heads,
+                   dim, vdim, taps, conv, a_log, dt_bias, gain, 1.3, 1e-5, one, conv_off, row_req, spans, who, got)
+        qkv, bg = torch.empty(n, channels, device=DEV), torch.empty(n, 2 * heads + groups, device=DEV)
+        o.gdn_prepare(proj, extra, extra + channels, extra + channels + heads, groups, heads, dim, vdim, taps, conv, a_log,
+                      dt_bias, many, conv_off, row_req, spans, who, qkv, bg)
+        raw = torch.zeros(n, heads * vdim, device=DEV)
+        o.gdn_scan(qkv, bg, groups, heads, dim, vdim, many, spans, who, raw)
+        want = torch.empty(n, heads * vdim, dtype=out_dtype, device=DEV)
+        o.gdn_out_norm(raw, proj, extra + channels + 2 * heads, gain, 1.3, 1e-5, want, heads, vdim, row_req)
+        close(got[:-1], want[:-1], out_dtype, f"step {step}")
+        assert torch.isnan(got[-1].float()).all()
+    close(one, many, torch.float32, "matrices and kept inputs")
+    assert float(one[3].abs().max()) > 0 and float(one[2].abs().max()) == 0
+
+
 def test_a_token_written_far_back_is_read_from_the_matrix():
     """Without decay and with keys at right angles, what token 3 wrote along its key comes back whole when
     token 900 asks along the same key; a matrix that lost it on the way (a portion's edge) gives zeros."""

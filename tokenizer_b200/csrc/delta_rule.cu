@@ -301,6 +301,110 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
   }
 }
 
+// ---- a step of single tokens: convolution, unit vectors, the recurrence's one token and the output
+// norm and gate in ONE kernel, a block a (row, head) with all of the head's columns (vdim * P threads).
+// The kept inputs are read here and moved on by gdn_conv_state, launched behind.
+template <int DPL, typename TI, typename TO>
+__global__ void __launch_bounds__(1024)
+gdn_step_kernel(const TI* __restrict__ proj, int ld, int qkv_at, int b_at, int a_at, int g_at, int groups, int heads,
+                int dim, int vdim, int taps, int P, const float* __restrict__ conv_w, const float* __restrict__ a_log,
+                const float* __restrict__ dt_bias, const float* __restrict__ gain, float out_scale, float eps,
+                float q_scale, float* __restrict__ state, long long state_stride, int conv_off,
+                const int* __restrict__ row_req, const int* __restrict__ state_slot, TO* __restrict__ out) {
+  extern __shared__ __align__(16) float gdn_one[];      // q [dim_p], k [dim_p], v [vdim], o [vdim], 8 scalars
+  __shared__ float scratch[33];
+  const int dim_p = P * DPL;
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int r = row_req[t];
+  pdl_wait();
+  pdl_launch();
+  if (r < 0) return;
+  float* q_s = gdn_one;
+  float* k_s = q_s + dim_p;
+  float* v_s = k_s + dim_p;
+  float* o_s = v_s + vdim;
+  float* misc = o_s + vdim;            // q scale, k scale, q . k, beta, decay
+  const int g = h / (heads / groups);
+  const int channels = 2 * groups * dim + heads * vdim;
+  const int slot = state_slot[r];
+  const float* kept = state + (size_t)slot * state_stride + conv_off;
+  const TI* row = proj + (size_t)t * ld;
+  // the head's 2 dim + vdim channels: the newest tap on this row, the others on the kept inputs
+  for (int i = threadIdx.x; i < 2 * dim_p + vdim; i += blockDim.x) {
+    const int which = i < dim_p ? 0 : i < 2 * dim_p ? 1 : 2;
+    const int l = i - which * dim_p;
+    float value = 0.f;
+    if (which == 2 || l < dim) {
+      const int c = which == 0 ? g * dim + l : which == 1 ? (groups + g) * dim + l : 2 * groups * dim + h * vdim + l;
+      float acc = conv_w[(size_t)c * taps + taps - 1] * to_float(row[qkv_at + c]);
+      for (int j = 0; j + 1 < taps; ++j) acc = fmaf(conv_w[(size_t)c * taps + j], kept[(size_t)j * channels + c], acc);
+      value = acc * gdn_sigmoid(acc);
+    }
+    gdn_one[i] = value;                 // q, k (zeros behind dim), v lie one behind the other
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < 3) {
+    const float* a = warp == 1 ? k_s : q_s;
+    const float* b = warp == 0 ? q_s : k_s;
+    float sum = 0.f;
+    for (int l = lane; l < dim; l += 32) sum = fmaf(a[l], b[l], sum);
+    sum = warp_sum(sum);
+    if (lane == 0) misc[warp] = warp == 2 ? sum : 1.0f / sqrtf(sum + 1e-6f);     // 0: |q|, 1: |k|, 2: q . k (raw)
+  } else if (warp == 3 && lane == 0) {
+    misc[3] = gdn_sigmoid(to_float(row[b_at + h]));
+    misc[4] = expf(-expf(a_log[h]) * gdn_softplus(to_float(row[a_at + h]) + dt_bias[h]));
+  }
+  __syncthreads();
+  const float q_unit = misc[0] * q_scale, k_unit = misc[1];
+  const float kq = misc[2] * q_unit * k_unit, beta = misc[3], decay = misc[4];
+  const int part = threadIdx.x % P, j = threadIdx.x / P;          // every thread has a column: vdim * P threads
+  const int piece = P * 4;
+  float* mine = state + (size_t)slot * state_stride + ((size_t)h * vdim + j) * dim_p + part * 4;
+  float dk[2] = {0.f, 0.f}, dq[2] = {0.f, 0.f};
+  float S[DPL], kk[DPL];
+#pragma unroll
+  for (int e = 0; e < DPL; e += 4) {
+    const float4 m = *reinterpret_cast<const float4*>(mine + (e >> 2) * piece);
+    const float4 a = *reinterpret_cast<const float4*>(k_s + part * 4 + (e >> 2) * piece);
+    const float4 b = *reinterpret_cast<const float4*>(q_s + part * 4 + (e >> 2) * piece);
+    S[e] = m.x; S[e + 1] = m.y; S[e + 2] = m.z; S[e + 3] = m.w;
+    kk[e] = a.x * k_unit; kk[e + 1] = a.y * k_unit; kk[e + 2] = a.z * k_unit; kk[e + 3] = a.w * k_unit;
+    dk[0] = fmaf(S[e], kk[e], dk[0]);
+    dk[1] = fmaf(S[e + 1], kk[e + 1], dk[1]);
+    dk[0] = fmaf(S[e + 2], kk[e + 2], dk[0]);
+    dk[1] = fmaf(S[e + 3], kk[e + 3], dk[1]);
+    dq[0] = fmaf(S[e], b.x * q_unit, dq[0]);
+    dq[1] = fmaf(S[e + 1], b.y * q_unit, dq[1]);
+    dq[0] = fmaf(S[e + 2], b.z * q_unit, dq[0]);
+    dq[1] = fmaf(S[e + 3], b.w * q_unit, dq[1]);
+  }
+  float dot = dk[0] + dk[1], read = dq[0] + dq[1];
+  const bool upper = P > 1 && (part & (P >> 1));
+  if (P > 1) {
+    float keep = upper ? read : dot;
+    keep += __shfl_xor_sync(0xffffffffu, upper ? dot : read, P >> 1);
+    for (int o = P >> 2; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+    dot = keep;
+    read = keep;
+  }
+  float u = beta * (v_s[j] - decay * dot);
+  if (P > 1) u = __shfl_sync(0xffffffffu, u, 0, P);
+#pragma unroll
+  for (int e = 0; e < DPL; e += 4)
+    *reinterpret_cast<float4*>(mine + (e >> 2) * piece) =
+        make_float4(fmaf(kk[e], u, decay * S[e]), fmaf(kk[e + 1], u, decay * S[e + 1]),
+                    fmaf(kk[e + 2], u, decay * S[e + 2]), fmaf(kk[e + 3], u, decay * S[e + 3]));
+  const float mine_out = fmaf(kq, u, decay * read);
+  if (part == (P >> 1)) o_s[j] = mine_out;
+  const float ss = block_sum(part == (P >> 1) ? mine_out * mine_out : 0.f, scratch);     // publishes o_s too
+  const float inv = (1.0f / sqrtf(ss / (float)vdim + eps)) * out_scale;
+  for (int l = threadIdx.x; l < vdim; l += blockDim.x) {
+    const float z = to_float(row[g_at + h * vdim + l]);
+    out[((size_t)t * heads + h) * vdim + l] = from_float<TO>(o_s[l] * inv * gain[l] * (z * gdn_sigmoid(z)));
+  }
+}
+
 template <typename TG, typename TO>
 __global__ void gdn_out_norm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, int ld, int g_at,
                                     const float* __restrict__ gain, float scale, float eps, TO* __restrict__ out,
@@ -363,6 +467,19 @@ TOKB200_API int tokb200_gdn_padded_dim(int dim) {
   return gdn_parts(dim, gdn_rows(dim)) * gdn_rows(dim);
 }
 
+static inline int gdn_conv_state(const void* proj, int proj_dtype, int ld, int qkv_at, int channels, int taps,
+                                 float* state, long long state_stride, int conv_off, const int* q_start,
+                                 const int* state_slot, int n_requests, cudaStream_t stream) {
+  if (taps == 1) return TOKB200_OK;
+  dim3 grid((channels + 127) / 128, n_requests);
+  if (proj_dtype == TOKB200_F32)
+    return launch_dependent(gdn_conv_state_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, ld, qkv_at,
+                            channels, taps, state, state_stride, conv_off, q_start, state_slot);
+  return launch_dependent(gdn_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
+                          (const __nv_bfloat16*)proj, ld, qkv_at, channels, taps, state, state_stride, conv_off,
+                          q_start, state_slot);
+}
+
 TOKB200_API int tokb200_gdn_prepare(const void* proj, int proj_dtype, int ld, int qkv_at, int b_at, int a_at,
                                     int groups, int heads, int dim, int vdim, int taps, const float* conv_w,
                                     const float* a_log, const float* dt_bias, float* state, long long state_stride,
@@ -389,14 +506,54 @@ TOKB200_API int tokb200_gdn_prepare(const void* proj, int proj_dtype, int ld, in
                               state_slot, q_scale, qkv_out, bg_out);
   else
     return TOKB200_BAD_DTYPE;
-  if (status != TOKB200_OK || taps == 1) return status;
-  dim3 grid((channels + 127) / 128, n_requests);
-  if (proj_dtype == TOKB200_F32)
-    return launch_dependent(gdn_conv_state_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, ld, qkv_at,
-                            channels, taps, state, state_stride, conv_off, q_start, state_slot);
-  return launch_dependent(gdn_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
-                          (const __nv_bfloat16*)proj, ld, qkv_at, channels, taps, state, state_stride, conv_off,
-                          q_start, state_slot);
+  if (status != TOKB200_OK) return status;
+  return gdn_conv_state(proj, proj_dtype, ld, qkv_at, channels, taps, state, state_stride, conv_off, q_start, state_slot,
+                        n_requests, stream);
+}
+
+// Whether a step of single tokens can run as one kernel: a block holds all of a head's columns.
+TOKB200_API int tokb200_gdn_step_supported(int dim, int vdim) {
+  if (dim <= 0 || dim > 1024 || vdim <= 0) return 0;
+  const int dpl = gdn_rows(dim), P = gdn_parts(dim, dpl);
+  const int threads = vdim * P;
+  return threads <= 1024 && threads % 32 == 0 && threads >= 128;
+}
+
+// One token a request (row t belongs to request row_req[t], whose state lies in state_slot[row_req[t]]).
+TOKB200_API int tokb200_gdn_step(const void* proj, int proj_dtype, int ld, int qkv_at, int b_at, int a_at, int g_at,
+                                 int groups, int heads, int dim, int vdim, int taps, const float* conv_w,
+                                 const float* a_log, const float* dt_bias, const float* gain, float out_scale, float eps,
+                                 float* state, long long state_stride, int conv_off, const int* row_req,
+                                 const int* q_start, const int* state_slot, int n_rows, int n_requests, void* out,
+                                 int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || n_requests <= 0) return TOKB200_OK;
+  if (groups <= 0 || heads <= 0 || heads % groups || taps < 1 || taps > GDN_MAX_TAPS || heads > 65535 ||
+      !tokb200_gdn_step_supported(dim, vdim))
+    return TOKB200_BAD_SIZE;
+  if (((uintptr_t)state & 15) || state_stride % 4) return TOKB200_BAD_ALIGNMENT;
+  const int channels = 2 * groups * dim + heads * vdim;
+  const int dpl = gdn_rows(dim), P = gdn_parts(dim, dpl);
+  const size_t smem = (size_t)(2 * P * dpl + 2 * vdim + 8) * sizeof(float);
+  const float q_scale = 1.0f / sqrtf((float)dim);
+  dim3 grid(n_rows, heads), block(vdim * P);
+  int status = TOKB200_BAD_DTYPE;
+#define LAUNCH(D, TI, TO)                                                                                            \
+  status = launch_dependent(gdn_step_kernel<D, TI, TO>, grid, block, smem, stream, (const TI*)proj, ld, qkv_at, b_at, \
+                            a_at, g_at, groups, heads, dim, vdim, taps, P, conv_w, a_log, dt_bias, gain, out_scale,  \
+                            eps, q_scale, state, state_stride, conv_off, row_req, state_slot, (TO*)out)
+#define BY_ROWS(TI, TO)            \
+  if (dpl == 8) LAUNCH(8, TI, TO); \
+  else if (dpl == 16) LAUNCH(16, TI, TO); \
+  else LAUNCH(32, TI, TO)
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) { BY_ROWS(float, float); }
+  else if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) { BY_ROWS(float, __nv_bfloat16); }
+  else if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) { BY_ROWS(__nv_bfloat16, __nv_bfloat16); }
+  else if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) { BY_ROWS(__nv_bfloat16, float); }
+#undef BY_ROWS
+#undef LAUNCH
+  if (status != TOKB200_OK) return status;
+  return gdn_conv_state(proj, proj_dtype, ld, qkv_at, channels, taps, state, state_stride, conv_off, q_start, state_slot,
+                        n_requests, stream);
 }
 
 TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, int heads, int dim, int vdim,

@@ -1199,6 +1199,29 @@ def gdn_scan(qkv: torch.Tensor, bg: torch.Tensor, groups: int, heads: int, dim: 
         _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _ptr(o_out), _stream()), "gdn_scan")
 
 
+def gdn_step_supported(dim: int, vdim: int) -> bool:
+    """Whether a step of single tokens runs as one kernel (a block holds all of a head's columns)."""
+    return bool(_lib("delta_rule").tokb200_gdn_step_supported(_i(dim), _i(vdim)))
+
+
+def gdn_step(proj: torch.Tensor, qkv_at: int, b_at: int, a_at: int, g_at: int, groups: int, heads: int, dim: int,
+             vdim: int, taps: int, conv_w, a_log, dt_bias, gain, scale: float, eps: float, state: torch.Tensor,
+             conv_off: int, row_req, q_start, state_slot, out: torch.Tensor) -> None:
+    """A step in which every request brings ONE token: what `gdn_prepare`, `gdn_scan` and `gdn_out_norm` do,
+    in one kernel (a block a row and head), then the kept inputs move on.  `out` [T, heads * vdim]."""
+    channels = 2 * groups * dim + heads * vdim
+    n = proj.shape[0]
+    if state.dtype != torch.float32 or state.dim() != 2 or tuple(out.shape) != (n, heads * vdim) or \
+            conv_w.numel() != channels * taps or conv_off + (taps - 1) * channels > state.shape[1] or \
+            gain.numel() != vdim or g_at + heads * vdim > proj.shape[1]:
+        raise ValueError("gdn_step: sizes of the state, the taps, the gain or the output disagree")
+    _check(_lib("delta_rule").tokb200_gdn_step(
+        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(qkv_at), _i(b_at), _i(a_at), _i(g_at), _i(groups), _i(heads),
+        _i(dim), _i(vdim), _i(taps), _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), _ptr(gain), _f(scale), _f(eps), _ptr(state),
+        _ll(state.shape[1]), _i(conv_off), _ptr(row_req), _ptr(q_start), _ptr(state_slot), _i(n), _i(q_start.shape[0] - 1),
+        _ptr(out), _i(_tag(out)), _stream()), "gdn_step")
+
+
 def gdn_out_norm(o: torch.Tensor, gate: torch.Tensor, g_at: int, gain: torch.Tensor, scale: float, eps: float,
                  out: torch.Tensor, heads: int, vdim: int, row_req) -> None:
     """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * gain * scale * silu(gate[t, g_at + h vdim ..])."""

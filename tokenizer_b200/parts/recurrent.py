@@ -11,6 +11,8 @@ along, see `take_side`); gates, candidate, recurrence and the product with silu 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.spec import ConfigError
@@ -96,6 +98,10 @@ class MinGRU(SideProjection):
         return self.out.forward(y, partials_ok=True)
 
 
+# TOKB200_GDN_STEP=separate runs a step of single tokens through the kernels for portions too
+_ONE_KERNEL_STEP = os.environ.get("TOKB200_GDN_STEP", "fused") != "separate"
+
+
 def stacked_rows(weights, multiple: int = 8):
     """The matrices one under the other, with zero rows behind them up to a whole `multiple` of rows
     (rows of the float32 product then start on 32 bytes)."""
@@ -164,6 +170,9 @@ class GatedDeltaNet:
         self.conv_off = self.heads * self.vdim * self.dim_padded
         self.state_floats = -(-(self.conv_off + (self.taps - 1) * self.channels) // 4) * 4
 
+    def shape_key(self, q_lens):
+        return "delta1" if max(q_lens) == 1 else "delta"
+
     def input_stack(self):
         """(the six input matrices one under the other, as stored; their bias: none)."""
         return torch.cat(self._stack, dim=0), None
@@ -179,6 +188,14 @@ class GatedDeltaNet:
         starting at `at`; the output is scaled by `out_scale` (in float32, before it is rounded for
         the output projection)."""
         n, c, h = ctx.n_tokens, self.channels, self.heads
+        if ctx.max_q_len == 1 and _ONE_KERNEL_STEP and ops.gdn_step_supported(self.dim, self.vdim):
+            # every request brings one token: one kernel a mixer instead of four (a decoding step is bound
+            # by its launches)
+            y = self.runtime.empty(n, h * self.vdim)
+            ops.gdn_step(proj, at, at + c, at + c + h, at + c + 2 * h, self.groups, h, self.dim, self.vdim, self.taps,
+                         self.conv_w, self.a_log, self.dt_bias, self.gain, out_scale, self.eps, cache.state,
+                         self.conv_off, ctx.row_req, ctx.q_start, ctx.state_slot, y)
+            return self.out.forward(y, partials_ok=True)
         qkv = torch.empty((n, c), dtype=torch.float32, device=proj.device)
         bg = torch.empty((n, 2 * h + self.groups), dtype=torch.float32, device=proj.device)
         ops.gdn_prepare(proj, at, at + c, at + c + h, self.groups, h, self.dim, self.vdim, self.taps, self.conv_w,
