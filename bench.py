@@ -998,7 +998,7 @@ def run_katopel(args):
                                                    a_log, dt_bias, state, conv_off, row_req, spans, slots, qkv, bg)),
                T * (channels + 2 * heads) * 8, "rope_store")
         record(f"gdn_scan, {T} tokens of {requests} request(s), {heads} heads of {dim} x {vdim}",
-               kernel_time(lambda: ops.gdn_scan(qkv, bg, groups, heads, dim, vdim, state, spans, slots, o)),
+               kernel_time(lambda: ops.gdn_scan(qkv, bg, groups, heads, dim, vdim, state, spans, slots, o, longest=T // requests)),
                T * (channels + 2 * heads + heads * vdim) * 4, "min_gru_scan", flops=T * heads * dim * vdim * 8)
     record(f"gdn_out_norm, {T} tokens x {heads} heads of {vdim}",
            kernel_time(lambda: ops.gdn_out_norm(o, proj, channels + 2 * heads, gain_v, 1.0, 1e-6, y16, heads, vdim, row_req)),

@@ -133,8 +133,10 @@ def run_in_portions(lengths, cuts, slots, fn):
 
 
 @pytest.mark.parametrize("groups,heads,dim,vdim,taps", [(2, 4, 16, 24, 4), (1, 1, 10, 6, 5), (3, 3, 64, 128, 2),
-                                                         (1, 2, 260, 8, 3), (2, 2, 8, 8, 1)])
-def test_the_delta_rule_in_portions_carries_matrices_and_kept_inputs(groups, heads, dim, vdim, taps):
+                                                         (1, 2, 260, 8, 3), (2, 2, 8, 8, 1), (2, 4, 128, 64, 4),
+                                                         (1, 2, 96, 20, 3)])
+@pytest.mark.parametrize("chunks", [False, True])
+def test_the_delta_rule_in_portions_carries_matrices_and_kept_inputs(groups, heads, dim, vdim, taps, chunks):
     """Three requests in slots that are not their indices, cut into portions of 1, 2 and many rows (shorter
     than the convolution too), against the recurrence token by token from each request's start."""
     o = ops()
@@ -159,7 +161,9 @@ def test_the_delta_rule_in_portions_carries_matrices_and_kept_inputs(groups, hea
         o.gdn_prepare(sub, extra, extra + channels, extra + channels + heads, groups, heads, dim, vdim, taps, conv,
                       a_log, dt_bias, state, conv_off, row_req, ints(spans), ints(who), qkv, bg)
         got = torch.empty(len(rows), heads * vdim, device=DEV)
-        o.gdn_scan(qkv, bg, groups, heads, dim, vdim, state, ints(spans), ints(who), got)
+        # asked to, heads of 65 to 128 lanes take the chunk form of the rule where a request brings 32 rows and more
+        o.gdn_scan(qkv, bg, groups, heads, dim, vdim, state, ints(spans), ints(who), got,
+                   longest=max(b - a for a, b in zip(spans, spans[1:])), chunks=chunks)
         out[idx] = got
 
     run_in_portions(lengths, cuts, slots, step)
@@ -217,11 +221,12 @@ def test_a_step_of_single_tokens_in_one_kernel(groups, heads, dim, vdim, taps, o
     assert float(one[3].abs().max()) > 0 and float(one[2].abs().max()) == 0
 
 
-def test_a_token_written_far_back_is_read_from_the_matrix():
+@pytest.mark.parametrize("dim,chunks", [(32, False), (128, False), (128, True)])
+def test_a_token_written_far_back_is_read_from_the_matrix(dim, chunks):
     """Without decay and with keys at right angles, what token 3 wrote along its key comes back whole when
     token 900 asks along the same key; a matrix that lost it on the way (a portion's edge) gives zeros."""
     o = ops()
-    dim, vdim, total = 32, 16, 901
+    vdim, total = 16, 901
     qkv = torch.zeros(total, 2 * dim + vdim, device=DEV)
     bg = torch.ones(total, 3, device=DEV)                  # beta 1, decay 1, and q . k (set below)
     for t in range(total):
@@ -239,7 +244,7 @@ def test_a_token_written_far_back_is_read_from_the_matrix():
     at = 0
     for n in (2, 2, 500, 1, 396):                           # the write and the read lie in different steps
         o.gdn_scan(qkv[at:at + n].contiguous(), bg[at:at + n].contiguous(), 1, 1, dim, vdim, state,
-                   ints([0, n]), ints([1]), out[at:at + n])
+                   ints([0, n]), ints([1]), out[at:at + n], longest=n, chunks=chunks)
         at += n
     assert torch.allclose(out[900], marker, atol=1e-5)
 

@@ -58,9 +58,9 @@ def tiny_a():
 
 def tiny_b():
     """Sizes the tensor-core kernels take (cache rows of 64 and 128 lanes), chunks of 100 that do not
-    fit the pages, a whole head rotated, a layer of plain causal attention without chunks, one expert
+    fit the pages, matrices of 96 rows, a whole head rotated, a layer of plain causal attention without chunks, one expert
     a token and no shared one; no loop."""
-    return config([parallel(attention(4, 2, 64, 64, 0.125, size=100, rot=(500.0, 64)), delta(2, 2, 64, 128, 4), 1.0, 0.5, moe(4, 1, 64)),
+    return config([parallel(attention(4, 2, 64, 64, 0.125, size=100, rot=(500.0, 64)), delta(2, 2, 96, 128, 4), 1.0, 0.5, moe(4, 1, 64)),
                    parallel(attention(2, 2, 128, 96, 0.09, rot=(1000000.0, 32)), delta(8, 2, 32, 32, 4), 0.4, 2.0, dense(256))],
                   vocab=1000, width=128, eps=1e-6, scale=1.0), 4, 16
 

@@ -301,6 +301,238 @@ gdn_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int
   }
 }
 
+// ---- the chunk form, for heads of 65 to 128 lanes (16 rows a thread, 8 parts a column) ----
+// Within a run of 16 tokens, with G_t the product of the run's decays up to token t and S0 the matrix
+// before the run, the rule unrolls to
+//     u_t = beta_t (v_t - G_t S0^T k_t - sum_{s<t} (G_t / G_s) (k_s . k_t) u_s)
+//     o_t = G_t S0^T q_t + sum_{s<=t} (G_t / G_s) (k_s . q_t) u_s
+//     S16 = G_15 S0 + sum_s (G_15 / G_s) k_s u_s^T
+// column by column.  The 32 sums against S0 are independent of one another (no chain from token to
+// token), their shares are added over a column's 8 lanes in one packed round that leaves lane p with
+// tokens 2 p and 2 p + 1; the scalars (G_t / G_s) (k_s . k_t) and (G_t / G_s) (k_s . q_t) are the same for
+// all columns and computed once a run by the block; what stays a chain is the triangular solve, one
+// shuffle and a few operations a token.  All 32-bit; only the order of the sums differs from the
+// token-by-token kernel.  Measured SLOWER than that kernel (0.75 against 0.62 ms for 2,048 tokens of 16
+// heads of 128 x 128): with a column's rows spread over 8 lanes every warp reads all of k and q of every
+// token from shared memory, here twice (the sums, the matrix's move) and once more for the scalars, and
+// the block's shared-memory reads (about 5,400 cycles a run of 16 tokens) bound it.  Off unless asked for.
+#define GDN_RUN 16
+
+__device__ __forceinline__ void gdn_compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GDN_SCAN_THREADS) : "memory"); }
+
+__global__ void __launch_bounds__(GDN_SCAN_THREADS + 32)
+gdn_scan_chunked_kernel(const float* __restrict__ qkv, const float* __restrict__ bg, int channels, int groups,
+                        int heads, int dim, int vdim, float* __restrict__ state, long long state_stride,
+                        const int* __restrict__ q_start, const int* __restrict__ state_slot,
+                        float* __restrict__ o_out) {
+  constexpr int DPL = 16, P = 8, dim_p = 128, cols = GDN_SCAN_THREADS / P, run = GDN_RUN;
+  extern __shared__ __align__(16) float gdn_stage[];
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int col0 = blockIdx.x * cols;
+  const int first = q_start[r], last = q_start[r + 1];
+  pdl_wait();
+  pdl_launch();
+  if (first >= last) return;
+  constexpr int per = run * (2 * dim_p + cols + 3);                // a multiple of 4
+  float* a_k = gdn_stage + 2 * per;      // [run][run]: (G_t / G_s) k_s . k_t below the diagonal, zero elsewhere
+  float* b_q = a_k + run * run;          // [run][run]: (G_t / G_s) k_s . q_t on and below the diagonal
+  float* g_c = b_q + run * run;          // [run]: G_t
+  float* r_l = g_c + run;                // [run]: G_15 / G_s
+  for (int i = threadIdx.x; i < 2 * per; i += blockDim.x) gdn_stage[i] = 0.f;
+  __syncthreads();
+  const int g = h / (heads / groups);
+  const int k_col = (groups + g) * dim, q_col = g * dim, v_col = 2 * groups * dim + h * vdim + col0;
+  const int n_cols = min(cols, vdim - col0);
+  const int n_runs = (last - first + run - 1) / run;
+  const int n_bg = 2 * heads + groups;
+
+  if (threadIdx.x >= GDN_SCAN_THREADS) {
+    // ---- the staging warp, a run ahead ----
+    const int lane = threadIdx.x - GDN_SCAN_THREADS;
+    const bool wide = dim % 4 == 0 && channels % 4 == 0 && k_col % 4 == 0 && q_col % 4 == 0 &&
+                      (((uintptr_t)qkv) & 15) == 0;
+    for (int c = 0; c <= n_runs; ++c) {
+      if (c < n_runs) {
+        float* k_s = gdn_stage + (size_t)(c & 1) * per;
+        float* q_s = k_s + run * dim_p;
+        float* v_s = q_s + run * dim_p;
+        float* b_s = v_s + run * cols;
+        const int t0 = first + c * run;
+        const int n = min(run, last - t0);
+        if (wide) {
+          const int quads = dim >> 2;
+          for (int i = lane; i < n * quads; i += 32) {
+            const int tok = i / quads, l = (i - tok * quads) * 4;
+            const float* row = qkv + (size_t)(t0 + tok) * channels;
+            gdn_copy16(&k_s[tok * dim_p + l], row + k_col + l);
+            gdn_copy16(&q_s[tok * dim_p + l], row + q_col + l);
+          }
+        } else {
+          for (int i = lane; i < n * dim; i += 32) {
+            const int tok = i / dim, l = i - tok * dim;
+            const float* row = qkv + (size_t)(t0 + tok) * channels;
+            gdn_copy4(&k_s[tok * dim_p + l], row + k_col + l);
+            gdn_copy4(&q_s[tok * dim_p + l], row + q_col + l);
+          }
+        }
+        for (int i = lane; i < n * n_cols; i += 32) {
+          const int tok = i / n_cols, l = i - tok * n_cols;
+          gdn_copy4(&v_s[tok * cols + l], qkv + (size_t)(t0 + tok) * channels + v_col + l);
+        }
+        for (int tok = lane; tok < run; tok += 32) {
+          if (tok < n) {
+            const float* row = bg + (size_t)(t0 + tok) * n_bg;
+            gdn_copy4(&b_s[tok], row + h);
+            gdn_copy4(&b_s[run + tok], row + heads + h);
+          } else {                        // tokens the run does not have: they write nothing and keep the matrix
+            b_s[tok] = 0.f;
+            b_s[run + tok] = 1.f;
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      __syncthreads();      // run c is in place; everybody is done with run c - 1
+    }
+    return;
+  }
+
+  const int part = threadIdx.x % P, col = threadIdx.x / P;
+  const int j = col0 + col;
+  const bool live = j < vdim;
+  constexpr int piece = P * 4;
+  float S[DPL];
+  float* mine = state + (size_t)state_slot[r] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim_p + part * 4;
+#pragma unroll
+  for (int e = 0; e < DPL; e += 4) {
+    const float4 v = live ? *reinterpret_cast<const float4*>(mine + (e >> 2) * piece) : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[e] = v.x; S[e + 1] = v.y; S[e + 2] = v.z; S[e + 3] = v.w;
+  }
+  __syncthreads();          // run 0 is in place
+  for (int c = 0; c < n_runs; ++c) {
+    const float* k_s = gdn_stage + (size_t)(c & 1) * per;
+    const float* q_s = k_s + run * dim_p;
+    const float* v_s = q_s + run * dim_p;
+    const float* b_s = v_s + run * cols;
+    const float* d_s = b_s + run;
+    const int n = min(run, last - first - c * run);
+    // ---- the run's scalars: 256 pairs (t, s) over the 128 threads; pair (t, s) is k_s . k_t below the
+    // diagonal and k_t . q_s on and above it (stored transposed) ----
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      const int idx = threadIdx.x + rep * GDN_SCAN_THREADS;
+      const int t = idx >> 4, s = idx & 15;
+      const bool lower = s < t;
+      const float* a = k_s + (lower ? s : t) * dim_p;
+      const float* b = lower ? k_s + t * dim_p : q_s + s * dim_p;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      if (t < n && s < n) {
+        // every lane starts at another piece of its rows: the lanes' rows lie a whole number of banks apart
+        for (int step = 0; step < dim_p / 4; ++step) {
+          const int l = ((step + (int)threadIdx.x) & (dim_p / 4 - 1)) * 4;
+          const float4 x = *reinterpret_cast<const float4*>(a + l), y = *reinterpret_cast<const float4*>(b + l);
+          d0 = fmaf(x.x, y.x, d0); d1 = fmaf(x.y, y.y, d1); d2 = fmaf(x.z, y.z, d2); d3 = fmaf(x.w, y.w, d3);
+        }
+      }
+      float ratio = 1.f;                                  // the decays between the two tokens
+      const int lo = lower ? s : t, hi = lower ? t : s;
+      for (int i = lo + 1; i <= hi; ++i) ratio *= d_s[i];
+      const float value = ((d0 + d1) + (d2 + d3)) * ratio;
+      if (lower) {
+        a_k[t * run + s] = value;
+        b_q[s * run + t] = 0.f;
+      } else {
+        b_q[s * run + t] = value;
+        a_k[t * run + s] = 0.f;
+      }
+    }
+    if (threadIdx.x < run) {
+      float up = 1.f, down = 1.f;
+      for (int i = 0; i <= threadIdx.x; ++i) up *= d_s[i];
+      for (int i = threadIdx.x + 1; i < run; ++i) down *= d_s[i];
+      g_c[threadIdx.x] = up;
+      r_l[threadIdx.x] = down;
+    }
+    // ---- this thread's shares of S0^T k_t and S0^T q_t, t = 0 .. 15 ----
+    float w[2 * GDN_RUN];
+#pragma unroll
+    for (int t = 0; t < run; ++t) {
+      float dk = 0.f, dq = 0.f;
+#pragma unroll
+      for (int e = 0; e < DPL; e += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(k_s + t * dim_p + part * 4 + (e >> 2) * piece);
+        const float4 y = *reinterpret_cast<const float4*>(q_s + t * dim_p + part * 4 + (e >> 2) * piece);
+        dk = fmaf(S[e], x.x, dk); dk = fmaf(S[e + 1], x.y, dk); dk = fmaf(S[e + 2], x.z, dk); dk = fmaf(S[e + 3], x.w, dk);
+        dq = fmaf(S[e], y.x, dq); dq = fmaf(S[e + 1], y.y, dq); dq = fmaf(S[e + 2], y.z, dq); dq = fmaf(S[e + 3], y.w, dq);
+      }
+      w[2 * t] = dk;
+      w[2 * t + 1] = dq;
+    }
+    // ---- one packed round over the column's 8 lanes: lane p ends with w[4 p .. 4 p + 3], the sums of
+    // tokens 2 p and 2 p + 1 ----
+    {
+      const bool hi4 = part & 4, hi2 = part & 2, hi1 = part & 1;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float got = __shfl_xor_sync(0xffffffffu, hi4 ? w[i] : w[i + 16], 4);
+        w[i] = (hi4 ? w[i + 16] : w[i]) + got;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float got = __shfl_xor_sync(0xffffffffu, hi2 ? w[i] : w[i + 8], 2);
+        w[i] = (hi2 ? w[i + 8] : w[i]) + got;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float got = __shfl_xor_sync(0xffffffffu, hi1 ? w[i] : w[i + 4], 1);
+        w[i] = (hi1 ? w[i + 4] : w[i]) + got;
+      }
+    }
+    gdn_compute_sync();       // the run's scalars are in place
+    // ---- the solve, token by token: the lane that owns token s computes u_s and hands it to the others ----
+    const int t_a = 2 * part, t_b = 2 * part + 1;
+    const float base_a = v_s[t_a * cols + col] - g_c[t_a] * w[0], base_b = v_s[t_b * cols + col] - g_c[t_b] * w[2];
+    const float beta_a = b_s[t_a], beta_b = b_s[t_b];
+    float corr_a = 0.f, corr_b = 0.f;                     // sum_{s<t} a_k[t][s] u_s
+    float out_a = g_c[t_a] * w[1], out_b = g_c[t_b] * w[3];
+    float u[GDN_RUN];
+#pragma unroll
+    for (int s = 0; s < run; ++s) {
+      const float mine_u = (s & 1) ? beta_b * (base_b - corr_b) : beta_a * (base_a - corr_a);
+      u[s] = __shfl_sync(0xffffffffu, mine_u, s >> 1, P);
+      corr_a = fmaf(a_k[t_a * run + s], u[s], corr_a);
+      corr_b = fmaf(a_k[t_b * run + s], u[s], corr_b);
+      out_a = fmaf(b_q[t_a * run + s], u[s], out_a);
+      out_b = fmaf(b_q[t_b * run + s], u[s], out_b);
+    }
+    if (live) {
+      float* o_row = o_out + (size_t)(first + c * run) * heads * vdim + h * vdim + j;
+      if (t_a < n) o_row[(size_t)t_a * heads * vdim] = out_a;
+      if (t_b < n) o_row[(size_t)t_b * heads * vdim] = out_b;
+    }
+    // ---- the matrix moves on by the whole run ----
+    const float g_all = g_c[run - 1];
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) S[e] *= g_all;
+#pragma unroll
+    for (int s = 0; s < run; ++s) {
+      const float scaled = u[s] * r_l[s];
+#pragma unroll
+      for (int e = 0; e < DPL; e += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(k_s + s * dim_p + part * 4 + (e >> 2) * piece);
+        S[e] = fmaf(x.x, scaled, S[e]); S[e + 1] = fmaf(x.y, scaled, S[e + 1]);
+        S[e + 2] = fmaf(x.z, scaled, S[e + 2]); S[e + 3] = fmaf(x.w, scaled, S[e + 3]);
+      }
+    }
+    __syncthreads();        // done with run c (and with its scalars); run c + 1 is in place
+  }
+  if (live) {
+#pragma unroll
+    for (int e = 0; e < DPL; e += 4)
+      *reinterpret_cast<float4*>(mine + (e >> 2) * piece) = make_float4(S[e], S[e + 1], S[e + 2], S[e + 3]);
+  }
+}
+
 // ---- a step of single tokens: convolution, unit vectors, the recurrence's one token and the output
 // norm and gate in ONE kernel, a block a (row, head) with all of the head's columns (vdim * P threads).
 // The kept inputs are read here and moved on by gdn_conv_state, launched behind.
@@ -558,7 +790,7 @@ TOKB200_API int tokb200_gdn_step(const void* proj, int proj_dtype, int ld, int q
 
 TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, int heads, int dim, int vdim,
                                  float* state, long long state_stride, const int* q_start, const int* state_slot,
-                                 int n_requests, float* o_out, cudaStream_t stream) {
+                                 int n_requests, int longest, int chunks, float* o_out, cudaStream_t stream) {
   if (n_requests <= 0) return TOKB200_OK;
   if (groups <= 0 || heads <= 0 || heads % groups || dim <= 0 || dim > 1024 || vdim <= 0 || heads > 65535 ||
       n_requests > 65535)
@@ -575,6 +807,13 @@ TOKB200_API int tokb200_gdn_scan(const float* qkv, const float* bg, int groups, 
   if (run < 1) return TOKB200_BAD_SIZE;
   const size_t smem = (size_t)2 * ((run * (2 * dim_p + cols + 3) + 3) / 4 * 4) * sizeof(float);
   dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
+  if (chunks && dpl == 16 && P == 8 && longest >= 2 * GDN_RUN) {
+    // asked for: portions of 32 tokens and more of heads of 65 to 128 lanes in the chunk form
+    constexpr int per = GDN_RUN * (2 * 128 + GDN_SCAN_THREADS / 8 + 3);
+    const size_t bytes = (size_t)(2 * per + 2 * GDN_RUN * GDN_RUN + 2 * GDN_RUN) * sizeof(float);
+    return launch_dependent(gdn_scan_chunked_kernel, grid, dim3(GDN_SCAN_THREADS + 32), bytes, stream, qkv, bg, channels,
+                            groups, heads, dim, vdim, state, state_stride, q_start, state_slot, o_out);
+  }
 #define LAUNCH(D)                                                                                               \
   return launch_dependent(gdn_scan_kernel<D>, grid, dim3(GDN_SCAN_THREADS + 32), smem, stream, qkv, bg, channels, \
                           groups, heads, dim, vdim, P, cols, run, state, state_stride, q_start, state_slot, o_out)

@@ -1184,11 +1184,18 @@ def gdn_prepare(proj: torch.Tensor, qkv_at: int, b_at: int, a_at: int, groups: i
         _stream()), "gdn_prepare")
 
 
+_GDN_CHUNKS = os.environ.get("TOKB200_GDN_SCAN", "tokens") == "chunks"
+
+
 def gdn_scan(qkv: torch.Tensor, bg: torch.Tensor, groups: int, heads: int, dim: int, vdim: int, state: torch.Tensor,
-             q_start, state_slot, o_out: torch.Tensor) -> None:
+             q_start, state_slot, o_out: torch.Tensor, longest: int = 1, chunks: Optional[bool] = None) -> None:
     """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over every request's rows,
     head by head; `state` float32 [slots, n] holds the heads' matrices transposed and padded
-    ([heads, vdim, gdn_padded_dim(dim)]) at the start of a slot; `o_out` float32 [T, heads * vdim]."""
+    ([heads, vdim, gdn_padded_dim(dim)]) at the start of a slot; `o_out` float32 [T, heads * vdim].  `longest`: the
+    most rows a request brings.  `chunks`: from 32 rows on, heads of 65 to 128 lanes run the chunk form of the rule
+    (the same sums in another order; measured slower, so it is off unless asked for here or by TOKB200_GDN_SCAN=chunks)."""
+    if chunks is None:
+        chunks = _GDN_CHUNKS
     n = qkv.shape[0]
     if state.dtype != torch.float32 or o_out.dtype != torch.float32 or tuple(o_out.shape) != (n, heads * vdim) or \
             qkv.shape[1] != 2 * groups * dim + heads * vdim or heads * vdim * gdn_padded_dim(dim) > state.shape[1] or \
@@ -1196,7 +1203,8 @@ def gdn_scan(qkv: torch.Tensor, bg: torch.Tensor, groups: int, heads: int, dim: 
         raise ValueError("gdn_scan: sizes of the state or the outputs disagree")
     _check(_lib("delta_rule").tokb200_gdn_scan(
         _ptr(qkv), _ptr(bg), _i(groups), _i(heads), _i(dim), _i(vdim), _ptr(state), _ll(state.shape[1]),
-        _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _ptr(o_out), _stream()), "gdn_scan")
+        _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _i(longest), _i(int(bool(chunks))), _ptr(o_out),
+        _stream()), "gdn_scan")
 
 
 def gdn_step_supported(dim: int, vdim: int) -> bool:

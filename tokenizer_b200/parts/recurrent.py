@@ -171,7 +171,8 @@ class GatedDeltaNet:
         self.state_floats = -(-(self.conv_off + (self.taps - 1) * self.channels) // 4) * 4
 
     def shape_key(self, q_lens):
-        return "delta1" if max(q_lens) == 1 else "delta"
+        longest = max(q_lens)
+        return "delta1" if longest == 1 else "delta" if longest < 32 else "delta32"      # the kernels' choices
 
     def input_stack(self):
         """(the six input matrices one under the other, as stored; their bias: none)."""
@@ -202,7 +203,8 @@ class GatedDeltaNet:
                         self.a_log, self.dt_bias, cache.state, self.conv_off, ctx.row_req, ctx.q_start,
                         ctx.state_slot, qkv, bg)
         o = torch.empty((n, h * self.vdim), dtype=torch.float32, device=proj.device)
-        ops.gdn_scan(qkv, bg, self.groups, h, self.dim, self.vdim, cache.state, ctx.q_start, ctx.state_slot, o)
+        ops.gdn_scan(qkv, bg, self.groups, h, self.dim, self.vdim, cache.state, ctx.q_start, ctx.state_slot, o,
+                     longest=ctx.max_q_len)
         y = self.runtime.empty(n, h * self.vdim)
         ops.gdn_out_norm(o, proj, at + c + 2 * h, self.gain, out_scale, self.eps, y, h, self.vdim, ctx.row_req)
         return self.out.forward(y, partials_ok=True)
