@@ -910,7 +910,7 @@ def katopel_config(z):
     delta = {"heads": z["d_heads"], "kv_heads": z["d_kv"], "dim": z["d_dim"], "vdim": z["d_vdim"], "conv": z["taps"]}
     left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
             "mask": {"size": z["chunk"]}, "rot": {"base": 1000000.0, "dims": z["rot"]}}
-    side = {"left": left, "right": delta, "left_scale": 0.6, "right_scale": 1.1}
+    side = {"left": left, "right": delta, "left_scale": 0.5, "right_scale": 1.25}
     pattern = [{"type": "delta", "mixer": delta, "mlp": dense}, {"type": "parallel", "mixer": side, "mlp": moe},
                {"type": "parallel", "mixer": side, "mlp": dense}, {"type": "delta", "mixer": delta, "mlp": moe}]
     return tb.config.KatopelConfig.from_dict({
@@ -1018,7 +1018,7 @@ def run_katopel(args):
            "rms_norm")
     two = rnd(2, T, H)
     record(f"post_norm_add of two scaled terms (float32 partial sums and bfloat16) with the next norm, {T} x {H}",
-           kernel_time(lambda: ops.post_norm_add(x, [(two, 0.6), (y, 1.1)], g1, b1, 1e-6, g1, b1, 1e-6, h16)),
+           kernel_time(lambda: ops.post_norm_add(x, [(two, 0.5), (y, 1.25)], g1, b1, 1e-6, g1, b1, 1e-6, h16)),
            T * H * (8 + 2 + 4 + 4 + 2), "rms_norm")
     nh, nkv, d = 16, 4, 128
     wide = rnd(T, (nh + 2 * nkv) * d + 64)

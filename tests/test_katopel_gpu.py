@@ -68,7 +68,7 @@ def test_the_norm_behind_a_sublayer_adds_and_norms_again(width, form, chained):
     elif form == "partials":
         terms = [(rnd(3, 5, width, seed=9), 1.0)]
     else:
-        terms = [(rnd(2, 5, width, seed=9), 0.6), (rnd(5, width, seed=10, dtype=torch.bfloat16), 1.7)]
+        terms = [(rnd(2, 5, width, seed=9), 0.7), (rnd(5, width, seed=10, dtype=torch.bfloat16), 1.7)]
     y = sum((t.double().cpu() if t.dim() == 2 else t.double().cpu().sum(0)) * s for t, s in terms)
     want_x = x.double().cpu() + plain.layer_norm(y, g1.double().cpu(), b1.double().cpu(), 1e-6)
     out = torch.empty(5, width, dtype=torch.bfloat16, device=DEV) if chained else None
@@ -251,7 +251,7 @@ def test_a_token_written_far_back_is_read_from_the_matrix(dim, chunks):
 
 # ---- queries, keys and values of unlike head sizes ---------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(4, 2, 64, 128, 32), (3, 3, 10, 20, 0), (4, 1, 32, 16, 32), (2, 2, 24, 24, 6)])
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(6, 2, 64, 128, 16), (3, 3, 10, 20, 0), (4, 1, 32, 16, 32), (2, 2, 24, 24, 6)])
 def test_bias_rotation_and_the_cache_write_with_padded_rows(heads, kv, dim, vdim, rot, dtype):
     o = ops()
     n, extra, row = 9, 8, -(-max(dim, vdim) // 16) * 16
@@ -328,10 +328,10 @@ def chunked_reference(q, dense, row_req, pos, heads, kv, chunk, scale):
 
 
 @pytest.mark.parametrize("kernel,dtype,heads,kv,row,chunk", [
-    ("generic", torch.float32, 3, 3, 48, 200), ("generic", torch.bfloat16, 4, 2, 144, 37), ("generic", torch.float32, 2, 1, 32, 1),
-    ("decode", torch.bfloat16, 4, 2, 32, 200), ("decode", torch.bfloat16, 16, 1, 64, 37), ("decode", torch.bfloat16, 2, 2, 128, 256),
-    ("tiles", torch.bfloat16, 3, 3, 48, 37), ("tiles", torch.bfloat16, 4, 2, 80, 200), ("tiles", torch.bfloat16, 2, 2, 16, 1),
-    ("wide", torch.bfloat16, 4, 2, 128, 200), ("wide", torch.bfloat16, 6, 3, 128, 37), ("wide", torch.bfloat16, 2, 1, 64, 128)])
+    ("generic", torch.float32, 3, 3, 48, 160), ("generic", torch.bfloat16, 4, 2, 144, 37), ("generic", torch.float32, 2, 1, 32, 1),
+    ("decode", torch.bfloat16, 4, 2, 32, 160), ("decode", torch.bfloat16, 16, 1, 64, 37), ("decode", torch.bfloat16, 2, 2, 128, 256),
+    ("tiles", torch.bfloat16, 3, 3, 48, 37), ("tiles", torch.bfloat16, 4, 2, 80, 160), ("tiles", torch.bfloat16, 2, 2, 16, 1),
+    ("wide", torch.bfloat16, 4, 2, 128, 160), ("wide", torch.bfloat16, 6, 3, 128, 37), ("wide", torch.bfloat16, 2, 1, 64, 128)])
 def test_keys_are_seen_inside_the_querys_own_chunk_in_every_attention_kernel(kernel, dtype, heads, kv, row, chunk):
     """The last key before every query's chunk and the first key inside it get a score that stands out
     (the query itself, scaled) and values of their own: one must be missing from the output, the other
@@ -395,7 +395,7 @@ def test_keys_are_seen_inside_the_querys_own_chunk_in_every_attention_kernel(ker
 
 # ---- routed experts ------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,shared", [(8, 4, True), (3, 3, True), (6, 1, False), (70, 5, True)])
+@pytest.mark.parametrize("experts,top,shared", [(8, 3, True), (3, 3, True), (6, 1, False), (70, 5, True)])
 def test_routing_shares_and_the_gate_of_all_experts_lanes(experts, top, shared, dtype):
     o = ops()
     n, hidden, ff, sff = 37, 50, 6, 10
