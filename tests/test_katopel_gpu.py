@@ -1,5 +1,5 @@
 """The Katopel decoder on the GPU against the plain restatement: each mechanism's kernels alone,
-then whole models (three tiny configurations of unlike sizes) whole, token by token, in portions,
+then whole models (four tiny configurations of unlike sizes) whole, token by token, in portions,
 in mixed batches on few pages and slots, and through the generation entry point."""
 import math
 
@@ -422,7 +422,8 @@ def test_routing_shares_and_the_gate_of_all_experts_lanes(experts, top, shared, 
 
 
 # ---- whole models -----------------------------------------------------------------------------------
-LENGTHS = {"a": [1, 2, 23, 100, 131, 49], "b": [5, 19, 97, 201, 260, 100], "c": [3, 40, 130, 64, 1, 90]}
+LENGTHS = {"a": [1, 2, 23, 100, 131, 49], "b": [5, 19, 97, 201, 260, 100], "c": [3, 40, 130, 64, 1, 90],
+           "d": [4, 31, 77, 150, 9, 60]}
 
 
 @pytest.fixture(scope="module", params=sorted(TINY))

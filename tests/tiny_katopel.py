@@ -74,7 +74,18 @@ def tiny_c():
                   vocab=77, width=50, eps=3e-6, scale=0.5, loop=(0, 2, 1)), 5, 32
 
 
-TINY = {"a": tiny_a, "b": tiny_b, "c": tiny_c}
+def tiny_d():
+    """Two layers of mixers side by side inside a loop that starts behind the first layer and ends before
+    the last: chunks of 7 (shorter than a page) and of 50 in two cache groups of unlike rows, a head
+    wider in its keys than in its values and rotated whole, one without a feed-forward, a delta rule
+    of one head."""
+    return config([delta(2, 1, 12, 20, 3, moe(5, 2, 16, shared=24)),
+                   parallel(attention(2, 2, 48, 16, 0.2, size=7, rot=(100.0, 48)), delta(4, 4, 16, 16, 2), 0.9, 0.8, dense(72)),
+                   parallel(attention(6, 3, 16, 32, 0.3, size=50, rot=(10000.0, 8)), delta(1, 1, 20, 12, 4), 1.2, 0.3),
+                   delta(2, 2, 32, 64, 4, dense(40))], vocab=120, width=64, eps=2e-6, scale=1.5, loop=(1, 3, 2)), 6, 16
+
+
+TINY = {"a": tiny_a, "b": tiny_b, "c": tiny_c, "d": tiny_d}
 # sharper attention, so that a key seen or missed moves the logits in bfloat16 too, and an embedding that
 # makes logits of a size against which a tolerance means something
 SHARPEN = {r"left\.q$": 6.0, r"^embed$": 5.0, r"\.router$": 5.0}
